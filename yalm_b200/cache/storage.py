@@ -18,6 +18,8 @@ equal share one *group*, which has storage of its own:
   sequence has one block of its own, ``K, V : [entries, slots, kv_heads, capacity,
   head_dim]``, no table: the decode attention streams from that layout 5 to 20 %
   faster (batch 8 to 64 at 7B sizes).
+  A need with ``values=False`` has one plane: its rows serve as keys and as values (a cached
+  latent), and the view's ``v`` is its ``k``.
 * ``state`` groups hold ``[entries, slots, *shape]`` of fixed size per
   sequence; it is zeroed when a slot is acquired.  The Llama / Mistral decoder
   declares none; the storage exists for mixers that carry a recurrent state.
@@ -54,12 +56,13 @@ class CacheNeed:
     head_dim: int = 0
     window: Optional[int] = None               # kv: keep only the last `window` positions
     every: int = 1                             # kv: one row per `every` positions (row r: block r)
+    values: bool = True                        # kv: False when a row serves as key AND value (one plane)
     state_shape: Tuple[int, ...] = ()          # state: per-sequence shape
     state_dtype: torch.dtype = torch.float32
 
     def group_key(self, context: int):
         if self.kind == "kv":
-            return ("kv", self.kv_heads, self.head_dim, self.capacity(context), self.every)
+            return ("kv", self.kv_heads, self.head_dim, self.capacity(context), self.every, self.values)
         return ("state", tuple(self.state_shape), self.state_dtype)
 
     def capacity(self, context: int) -> int:
@@ -155,12 +158,12 @@ class Cache:
                 if n_pages == 0:                                   # one block per sequence
                     shape = (n, n_slots, need.kv_heads, cap, need.head_dim)
                     g["k"] = torch.zeros(shape, dtype=dtype, device=self.device)
-                    g["v"] = torch.zeros(shape, dtype=dtype, device=self.device)
+                    g["v"] = torch.zeros(shape, dtype=dtype, device=self.device) if need.values else g["k"]
                     continue
                 shape = (n, need.kv_heads, n_pages, PAGE, need.head_dim)
                 g["pages_per_slot"] = -(-cap // PAGE)
                 g["k"] = torch.zeros(shape, dtype=dtype, device=self.device)
-                g["v"] = torch.zeros(shape, dtype=dtype, device=self.device)
+                g["v"] = torch.zeros(shape, dtype=dtype, device=self.device) if need.values else g["k"]
                 g["pool"] = SlotAllocator(n_pages, what="page")
                 g["held"] = [[] for _ in range(n_slots)]           # a slot's pages, in row order
                 table = torch.zeros((n_slots, g["pages_per_slot"]), dtype=torch.int32)
@@ -179,7 +182,7 @@ class Cache:
         total = 0
         for g in self.groups:
             for name in ("k", "v", "state"):
-                if name in g:
+                if name in g and not (name == "v" and g["v"] is g["k"]):
                     total += g[name].numel() * g[name].element_size()
         return total
 
@@ -192,7 +195,7 @@ class Cache:
             if need.kind == "kv":
                 pages = _pool_pages(need, n_slots, context, max_tokens)
                 rows = pages * PAGE if pages else n_slots * need.capacity(context)
-                total += 2 * rows * need.kv_heads * need.head_dim * esz
+                total += (2 if need.values else 1) * rows * need.kv_heads * need.head_dim * esz
             else:
                 n = 1
                 for s in need.state_shape:

@@ -12,6 +12,7 @@ from typing import Any, Dict
 
 from .golulix import GolulixConfig
 from .llama import ConfigError, LlamaConfig
+from .nekotar import NekotarConfig
 from .rudazen import RudazenConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -52,3 +53,4 @@ register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("MistralForCausalLM", LlamaConfig)
 register_architecture("Golulix", GolulixConfig)
 register_architecture("Rudazen", RudazenConfig)
+register_architecture("Nekotar", NekotarConfig)

@@ -188,6 +188,13 @@ int yalm_attention_pooled(const void* q, const void* kv_step, const void* k_cach
                           int nsplit, const int* page_table, int pages_per_slot, int n_pages,
                           const void* pool_k, const void* pool_v, int pool, int pool_capacity,
                           const int* pool_table, int pool_pps, int pool_pages, cudaStream_t stream);
+// yalm_attention with a window that keeps the first `keep` positions visible beside the last `window`
+int yalm_attention_keep_first(const void* q, const void* kv_step, const void* k_cache, const void* v_cache,
+                              const int* token_seq, const int* q_start, const int* seq_slot,
+                              const int* slot_pos, void* out, float* part_o, float* part_ml, int dtype,
+                              int n_tokens, int H, int G, int hd, int capacity, int window, int keep,
+                              float scale, int nsplit, const int* page_table, int pages_per_slot,
+                              int n_pages, cudaStream_t stream);
 
 // Prefill attention with 32-bit softmax weights on tensor cores (attention_exact.cu; dtype 1 or 2,
 // head size 32, 64 or 128, window >= 0): S = Q K^T by mma.sync, softmax in 32 bits, P split into
@@ -207,7 +214,7 @@ int yalm_attention_exact_prefill(const void* q, const void* kv_step, const void*
 // pos * freq[i] (freq [dims / 2]), pairs (i, i + dims/2), or (2i, 2i+1) with `neighbours`; cos and
 // sin are multiplied by `mult`.  Values: the v rows, or without them the keys as projected.
 int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long long partial_stride,
-                            const float* q_norm, const float* k_norm, int n_q, int n_k, float eps,
+                            const float* bias, const float* q_norm, const float* k_norm, int n_q, int n_k, float eps,
                             const float* freq, int dims, int neighbours, float mult,
                             const int* token_seq, const int* q_start, const int* seq_slot,
                             const int* slot_pos, void* q_out, void* kv_step, void* k_cache,
@@ -292,6 +299,47 @@ int yalm_glu_clamp(const float* gu, int n_partials, long long partial_stride, vo
                    cudaStream_t stream);
 int yalm_routed_combine(float* x, const float* y, const int* pair_row, const float* weight,
                         int n_tokens, int top, int dim, cudaStream_t stream);
+
+// ---- hyper.cu: several residual copies per token -----------------------------------------------
+// X [copies][rows][dim] float32.  Write (y not null): X_j <- sum_i mix[i][j] X_i + mult out_w[j] y, y the
+// sum of n_partials slices.  Read (in_w not null): u = sum_i in_w[i] X_i, normed with norm_w into h
+// (h_dtype), or without norm_w stored to u_out as float32.
+int yalm_hc_step(float* X, int copies, long long rows, int dim, const float* y, int n_partials,
+                 long long partial_stride, const float* mix, const float* out_w, float mult,
+                 const float* in_w, const float* norm_w, float eps, void* h, int h_dtype, float* u_out,
+                 cudaStream_t stream);
+
+// ---- recurrence.cu: o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_(t-1) + k_t v_t^T ------
+int yalm_token_shift(const void* h, const float* prev, const float* mu, void* out, int dtype,
+                     const int* token_seq, const int* q_start, const int* seq_slot, int n_tokens, int dim,
+                     int n_mix, cudaStream_t stream);
+int yalm_wkv(const float* r, int nr, long long sr, const float* k, int nk, long long sk, const float* v,
+             int nv, long long sv, const float* g, int ng, long long sg, const float* z, int nz,
+             long long sz, const float* w0, const float* bonus, float* act, float* gate, const void* h,
+             int h_dtype, float* prev, const int* token_seq, const int* q_start, const int* seq_slot,
+             float* state, float* out, int n_tokens, int n_seqs, int H, int dk, int dv, int dim,
+             cudaStream_t stream);
+int yalm_wkv_out(const float* o, const float* w, const float* gate, void* out, int out_dtype,
+                 long long rows, int heads, int size, float eps, cudaStream_t stream);
+
+// ---- latent.cu: attention over a cached latent ---------------------------------------------------
+int yalm_latent_store(const float* dkv, int n_partials, long long partial_stride, const float* c_norm,
+                      float eps, const float* freq, const int* token_seq, const int* q_start,
+                      const int* seq_slot, const int* slot_pos, void* kv_step, void* cache, int dtype,
+                      int n_tokens, int rank, int rd, int hd, int capacity, int write_cache,
+                      const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
+int yalm_latent_absorb_q(const float* q, int n_partials, long long partial_stride, const void* w_uk,
+                         const float* freq, const int* token_seq, const int* q_start, const int* seq_slot,
+                         const int* slot_pos, void* q_out, int dtype, int n_tokens, int H, int dim, int rd,
+                         int rank, int hd, cudaStream_t stream);
+int yalm_latent_expand(const void* o, const void* w_uv, const float* gate, int n_partials,
+                       long long partial_stride, void* out, int dtype, int n_tokens, int H, int rank,
+                       int vdim, int hd, cudaStream_t stream);
+
+// ---- small_ops.cu ---------------------------------------------------------------------------------
+// out [n] = act(sum of n_partials slices of z [n]): act 1 = gelu (tanh form), 2 = tanh
+int yalm_activation_rows(const float* z, int n_partials, long long partial_stride, void* out,
+                         int out_dtype, long long n, int act, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

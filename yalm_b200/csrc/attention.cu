@@ -93,6 +93,7 @@ struct PoolArgs {
   const void* v;
   const int* table;
   int pps, n_pages, capacity, pool;
+  int keep;                // > 0: beside its window a query also sees the positions below `keep`
 };
 __host__ __device__ __forceinline__ int pooled_visible(int pos, int window, int pool) {
   if (pool <= 0 || window <= 0) return 0;
@@ -133,9 +134,11 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
   const int qs = q_start[b];
   const int pos = past + (t - qs);
   const int lo = first_visible(pos, window);
-  // the keys in one numbering: the visible pooled blocks first, then the positions lo .. pos
+  // the keys in one numbering: the visible pooled blocks first, ...
   const int nb = pooled_visible(pos, window, pl.pool);
-  const int nkeys = nb + pos - lo + 1;
+  // ... then the kept first positions that lie before the window (at their own positions)
+  const int nfront = nb + (pl.keep > 0 ? min(pl.keep, lo) : 0);
+  const int nkeys = nfront + pos - lo + 1;
   const int per = (nkeys + nsplit - 1) / nsplit;
   const int s_lo = split * per;
   const int s_hi = min((split + 1) * per, nkeys);
@@ -176,7 +179,7 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
 #pragma unroll
     for (int u = 0; u < ATT_U; ++u) {
       const int idx = base + u * GROUPS + kg;
-      const int key = lo + idx - nb;
+      const int key = idx < nfront ? idx - nb : lo + idx - nfront;
       valid[u] = idx < s_hi;
       if (valid[u] && lane_on) {
         const T *kp, *vp;
@@ -646,10 +649,27 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
                               int capacity, int window, float scale, int nsplit,
                               const int* page_table, int pages_per_slot, int n_pages,
                               cudaStream_t stream) {
-  const PoolArgs none = {nullptr, nullptr, nullptr, 0, 0, 0, 0};
+  const PoolArgs none = {nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
   return attention_any(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
                        part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, scale, nsplit,
                        page_table, pages_per_slot, n_pages, none, stream);
+}
+
+// yalm_attention with a sliding window (window > 0) that keeps the first `keep` positions of a
+// sequence visible, at their own positions, beside the last `window`; the cache holds every
+// position (capacity: the context), not a ring.
+extern "C" int yalm_attention_keep_first(const void* q, const void* kv_step, const void* k_cache,
+                                         const void* v_cache, const int* token_seq, const int* q_start,
+                                         const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                                         float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
+                                         int capacity, int window, int keep, float scale, int nsplit,
+                                         const int* page_table, int pages_per_slot, int n_pages,
+                                         cudaStream_t stream) {
+  if (window <= 0 || keep < 0) return -2;
+  const PoolArgs pl = {nullptr, nullptr, nullptr, 0, 0, 0, 0, keep};
+  return attention_any(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
+                       part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, scale, nsplit,
+                       page_table, pages_per_slot, n_pages, pl, stream);
 }
 
 // yalm_attention with pooled blocks beside the window (window > 0): pool_k / pool_v hold one row
@@ -664,7 +684,7 @@ extern "C" int yalm_attention_pooled(const void* q, const void* kv_step, const v
                                      const int* pool_table, int pool_pps, int pool_pages,
                                      cudaStream_t stream) {
   if (pool <= 0 || window <= 0 || pool_capacity <= 0) return -2;
-  const PoolArgs pl = {pool_k, pool_v, pool_table, pool_pps, pool_pages, pool_capacity, pool};
+  const PoolArgs pl = {pool_k, pool_v, pool_table, pool_pps, pool_pages, pool_capacity, pool, 0};
   return attention_any(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
                        part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, scale, nsplit,
                        page_table, pages_per_slot, n_pages, pl, stream);

@@ -98,7 +98,7 @@ _SIGNATURES = {
                               _i, _i, _f, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_exact_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                                      _f, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
-    "yalm_qk_norm_rope_store": [_vp, _i, _ll, _vp, _vp, _i, _i, _f, _vp, _i, _i, _f, _vp, _vp, _vp, _vp,
+    "yalm_qk_norm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _vp, _i, _i, _f, _vp, _vp, _vp, _vp,
                                 _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_pool_blocks": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i,
                          _i, _vp, _i, _i, _vp, _vp],
@@ -107,6 +107,18 @@ _SIGNATURES = {
     "yalm_cast_rows": [_vp, _vp, _i, _ll, _vp],
     "yalm_head_norm": [_vp, _vp, _vp, _i, _ll, _i, _i, _f, _vp],
     "yalm_gated_recurrence": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "yalm_attention_keep_first": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                                  _i, _i, _i, _f, _i, _vp, _i, _i, _vp],
+    "yalm_hc_step": [_vp, _i, _ll, _i, _vp, _i, _ll, _vp, _vp, _f, _vp, _vp, _f, _vp, _i, _vp, _vp],
+    "yalm_token_shift": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "yalm_wkv": [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _ll, _vp, _i, _ll, _vp, _i, _ll, _vp, _vp, _vp, _vp,
+                 _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "yalm_wkv_out": [_vp, _vp, _vp, _vp, _i, _ll, _i, _i, _f, _vp],
+    "yalm_latent_store": [_vp, _i, _ll, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                          _i, _vp, _i, _i, _vp],
+    "yalm_latent_absorb_q": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "yalm_latent_expand": [_vp, _vp, _vp, _i, _ll, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "yalm_activation_rows": [_vp, _i, _ll, _vp, _i, _ll, _i, _vp],
 }
 
 _lib = None
@@ -302,10 +314,12 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
               capacity: int, window: Optional[int], nsplit: int = 1,
               part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
               pages=None, chunk: Optional[int] = None, scale: Optional[float] = None,
-              pooled=None) -> None:
+              pooled=None, keep_first: Optional[int] = None) -> None:
     """``pooled`` = (pool_k, pool_v, pool, pool_capacity, pool_pages): one (mean key, mean value)
     row per block of ``pool`` positions, seen beside the window by the queries it lies wholly
-    before (see ``pool_blocks``)."""
+    before (see ``pool_blocks``).  ``keep_first`` = F (with a window): the positions below F stay
+    visible, at their own positions, beside the last ``window``; the cache then holds every position
+    (``capacity`` is the context, not the window)."""
     n = q.shape[0]
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype,
@@ -329,6 +343,14 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
             G, hd, capacity, int(window), float(scale or 0.0), nsplit, pt, pps, npg, _p(pool_k),
             _p(pool_v), int(pool), int(pool_cap), ppt, ppps, pnpg, _stream()), "attention (pooled)",
             kernels=2 if nsplit > 1 else 1)
+        return
+    if keep_first:
+        _need(window and not chunk, "attention: kept first positions go with a sliding window")
+        _check(lib().yalm_attention_keep_first(
+            _p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq), _p(batch.q_start),
+            _p(batch.seq_slot), _p(slot_pos), _p(out), _p(part_o), _p(part_ml), dtype_code(q.dtype), n, H,
+            G, hd, capacity, int(window), int(keep_first), float(scale or 0.0), nsplit, pt, pps, npg,
+            _stream()), "attention (kept first positions)", kernels=2 if nsplit > 1 else 1)
         return
     _check(lib().yalm_attention(_p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq),
                                 _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), _p(out),
@@ -725,7 +747,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_partials: int, q_norm: Optional[torc
                        freq: torch.Tensor, dims: int, neighbours: bool, mult: float, batch,
                        q_out: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
                        v_cache: torch.Tensor, slot_pos: torch.Tensor, H: int, G: int, hd: int,
-                       has_v: bool, capacity: int, write_cache: bool = True, pages=None) -> None:
+                       has_v: bool, capacity: int, write_cache: bool = True, pages=None,
+                       bias: Optional[torch.Tensor] = None) -> None:
     """qkv float32 [(s,) N, (H + G (+ G)) hd] -> q_out [N, H hd], kv_step [N, 2, G, hd] and the cache
     rows: q and k normed over their whole rows (n_q, n_k true features), the first ``dims``
     features of each head rotated (pairs (i, i + dims/2), or (2i, 2i+1) with ``neighbours``), cos
@@ -743,8 +766,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_partials: int, q_norm: Optional[torc
     _need(q_out.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype and q_out.is_contiguous()
           and kv_step.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(),
           "qk_norm_rope_store: outputs of one type, contiguous")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == row and bias.is_contiguous()),
+          "qk_norm_rope_store: bias float32 [row]")
     _check(lib().yalm_qk_norm_rope_store(
-        _p(qkv), n_partials, n * row, _p(q_norm), _p(k_norm), int(n_q), int(n_k), float(eps), _p(freq),
+        _p(qkv), n_partials, n * row, _p(bias), _p(q_norm), _p(k_norm), int(n_q), int(n_k), float(eps), _p(freq),
         int(dims), 1 if neighbours else 0, float(mult), _p(batch.token_seq), _p(batch.q_start),
         _p(batch.seq_slot), _p(slot_pos), _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache),
         dtype_code(q_out.dtype), n, H, G, hd, 1 if has_v else 0, capacity, 1 if write_cache else 0, pt,
@@ -831,6 +856,144 @@ def gated_recurrence(proj: torch.Tensor, n_partials: int, f_bias: torch.Tensor, 
     _check(lib().yalm_gated_recurrence(_p(proj), n_partials, n * row, _p(f_bias), _p(lower), _p(act),
                                        _p(batch.q_start), _p(batch.seq_slot), _p(state), _p(out), n,
                                        batch.n_seqs, H, dk, dv, _stream()), "gated_recurrence", kernels=2)
+
+
+# ---- several residual copies per token --------------------------------------------------------
+def hc_step(X: torch.Tensor, write=None, read=None) -> None:
+    """X float32 [copies, N, dim].  ``write`` = (slices float32 [S, N, dim], S, mix [copies, copies]
+    (from, to), out [copies], mult): X_j <- sum_i mix[i, j] X_i + mult out[j] y.  ``read`` =
+    (in [copies], norm weight or None, eps, destination): u = sum_i in[i] X_i of the new X, normed
+    into the destination (any storage type), or without a norm weight stored as it is (float32)."""
+    s, n, dim = X.shape
+    _need(X.dtype == torch.float32 and X.is_contiguous() and 1 <= s <= 8, "hc_step: X float32 [1..8, N, dim]")
+    y = mix = out_w = in_w = norm_w = dst = None
+    S, mult, eps = 0, 0.0, 0.0
+    if write is not None:
+        y, S, mix, out_w, mult = write
+        _need(y.dtype == torch.float32 and y.is_contiguous() and y.numel() >= S * n * dim
+              and mix.dtype == out_w.dtype == torch.float32 and mix.numel() == s * s and out_w.numel() == s
+              and mix.is_contiguous(), "hc_step: slices float32 [S, N, dim], mix [s, s], out [s]")
+    if read is not None:
+        in_w, norm_w, eps, dst = read
+        _need(in_w.dtype == torch.float32 and in_w.numel() == s and dst.is_contiguous()
+              and dst.numel() == n * dim, "hc_step: in [s], destination [N, dim]")
+        _need(norm_w is not None or dst.dtype == torch.float32, "hc_step: an unnormed read is float32")
+        _need(norm_w is None or (norm_w.dtype == torch.float32 and norm_w.numel() == dim), "hc_step: norm weight")
+    normed = norm_w is not None
+    _check(lib().yalm_hc_step(_p(X), s, n, dim, _p(y), int(S), n * dim, _p(mix), _p(out_w), float(mult),
+                              _p(in_w), _p(norm_w), float(eps), _p(dst) if normed else None,
+                              dtype_code(dst.dtype) if normed else F32,
+                              None if (normed or dst is None) else _p(dst), _stream()), "hc_step")
+
+
+# ---- a recurrence with a decay per channel and a bonus for the current token ---------------------
+def token_shift(h: torch.Tensor, prev: torch.Tensor, mu: torch.Tensor, out: torch.Tensor, batch) -> None:
+    """out [n_mix, N, dim] = h + (h' - h) mu[s], h' the previous token's row of h; for a step's first
+    token the sequence's row of ``prev`` float32 [slots, dim]."""
+    n, dim = h.shape
+    n_mix = mu.shape[0]
+    _need(h.is_contiguous() and out.dtype == h.dtype and out.is_contiguous() and out.numel() == n_mix * n * dim
+          and mu.dtype == prev.dtype == torch.float32 and mu.is_contiguous() and mu.shape[1] == dim
+          and prev.is_contiguous() and prev.shape[1] == dim, "token_shift: shapes")
+    _check(lib().yalm_token_shift(_p(h), _p(prev), _p(mu), _p(out), dtype_code(h.dtype), _p(batch.token_seq),
+                                  _p(batch.q_start), _p(batch.seq_slot), n, dim, n_mix, _stream()),
+           "token_shift")
+
+
+def wkv(r, k, v, g, z, w0: torch.Tensor, bonus: torch.Tensor, act: torch.Tensor, gate: torch.Tensor,
+        h: torch.Tensor, prev: torch.Tensor, batch, state: torch.Tensor, out: torch.Tensor, H: int, dk: int,
+        dv: int) -> None:
+    """o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_(t-1) + k_t v_t^T per head over a
+    step's tokens.  r, k, z: (float32 slices [S, N, H dk], S); v, g: (slices [S, N, H dv], S);
+    w = exp(-exp(z + w0)); ``gate`` receives silu(g); ``state`` float32 [slots, H, dk, dv]; ``prev``
+    float32 [slots, dim] receives every sequence's last row of ``h``; out float32 [N, H dv]."""
+    n = out.shape[0]
+    row = 3 * H * dk + H * dv
+    args = []
+    for (buf, S), width in ((r, H * dk), (k, H * dk), (v, H * dv), (g, H * dv), (z, H * dk)):
+        _need(buf.dtype == torch.float32 and buf.is_contiguous() and buf.shape[-1] == width
+              and buf.shape[-2] == n, "wkv: projections as float32 slices [(s,) N, width]")
+        args += [_p(buf), int(S), n * width]
+    _need(w0.dtype == bonus.dtype == torch.float32 and w0.numel() == bonus.numel() == H * dk
+          and act.dtype == gate.dtype == torch.float32 and act.numel() >= n * row and gate.numel() >= n * H * dv
+          and state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv)
+          and out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == H * dv
+          and prev.dtype == torch.float32 and prev.is_contiguous() and prev.shape[1] == h.shape[1]
+          and h.is_contiguous() and h.shape[0] == n, "wkv: shapes")
+    _check(lib().yalm_wkv(*args, _p(w0), _p(bonus), _p(act), _p(gate), _p(h), dtype_code(h.dtype), _p(prev),
+                          _p(batch.token_seq), _p(batch.q_start), _p(batch.seq_slot), _p(state), _p(out), n,
+                          batch.n_seqs, H, dk, dv, h.shape[1], _stream()), "wkv", kernels=2)
+
+
+def wkv_out(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, heads: int,
+            size: int, eps: float) -> None:
+    """out [N, heads * size] = every head of o (float32) over its root mean square, times weight
+    [heads * size], times gate (float32 [N, heads * size])."""
+    n = o.shape[0]
+    _need(o.dtype == gate.dtype == weight.dtype == torch.float32 and o.is_contiguous() and gate.is_contiguous()
+          and o.shape[1] == heads * size and weight.numel() == heads * size and gate.numel() >= n * heads * size
+          and out.is_contiguous() and tuple(out.shape) == (n, heads * size), "wkv_out: shapes")
+    _check(lib().yalm_wkv_out(_p(o), _p(weight), _p(gate), _p(out), dtype_code(out.dtype), n, heads, size,
+                              float(eps), _stream()), "wkv_out")
+
+
+# ---- attention over a cached latent ----------------------------------------------------------------
+def latent_store(dkv: torch.Tensor, n_partials: int, c_norm: torch.Tensor, eps: float, freq: torch.Tensor,
+                 batch, slot_pos: torch.Tensor, kv_step: torch.Tensor, cache: torch.Tensor, rank: int,
+                 rd: int, hd: int, capacity: int, write_cache: bool = True, pages=None) -> None:
+    """dkv float32 [(s,) N, rank + rd] -> the row [norm(c) w | rot(kr) | 0] of every token, to
+    kv_step [N, 2, 1, hd] (key and value alike) and to the cache."""
+    n = kv_step.shape[0]
+    pt, pps, npg = _pages(pages, cache, 1, hd)
+    _need(dkv.dtype == torch.float32 and dkv.is_contiguous() and dkv.shape[-1] == rank + rd
+          and dkv.shape[-2] == n and c_norm.dtype == freq.dtype == torch.float32 and c_norm.numel() == rank
+          and freq.numel() >= max(1, rd // 2) and kv_step.dtype == cache.dtype and kv_step.is_contiguous()
+          and kv_step.numel() == n * 2 * hd and cache.is_contiguous(), "latent_store: shapes")
+    _check(lib().yalm_latent_store(_p(dkv), n_partials, n * (rank + rd), _p(c_norm), float(eps), _p(freq),
+                                   _p(batch.token_seq), _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
+                                   _p(kv_step), _p(cache), dtype_code(cache.dtype), n, rank, rd, hd, capacity,
+                                   1 if write_cache else 0, pt, pps, npg, _stream()), "latent_store")
+
+
+def latent_absorb_q(q: torch.Tensor, n_partials: int, w_uk: torch.Tensor, freq: torch.Tensor, batch,
+                    slot_pos: torch.Tensor, q_out: torch.Tensor, H: int, dim: int, rd: int, rank: int,
+                    hd: int) -> None:
+    """q float32 [(s,) N, H (dim + rd)], w_uk [H, dim, rank] -> q_out [N, H, hd] =
+    [Wuk_h^T q_h[:dim] | rot(q_h[dim:]) | 0]."""
+    n = q_out.shape[0]
+    _need(q.dtype == torch.float32 and q.is_contiguous() and q.shape[-1] == H * (dim + rd) and q.shape[-2] == n
+          and w_uk.dtype == q_out.dtype and w_uk.is_contiguous() and w_uk.numel() == H * dim * rank
+          and q_out.is_contiguous() and q_out.numel() == n * H * hd and freq.dtype == torch.float32,
+          "latent_absorb_q: shapes")
+    _check(lib().yalm_latent_absorb_q(_p(q), n_partials, n * H * (dim + rd), _p(w_uk), _p(freq),
+                                      _p(batch.token_seq), _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
+                                      _p(q_out), dtype_code(q_out.dtype), n, H, dim, rd, rank, hd, _stream()),
+           "latent_absorb_q")
+
+
+def latent_expand(o: torch.Tensor, w_uv: torch.Tensor, gate: Optional[torch.Tensor], n_partials: int,
+                  out: torch.Tensor, H: int, rank: int, vdim: int, hd: int) -> None:
+    """o [N, H, hd], w_uv [H, rank, vdim] -> out [N, H vdim] = (Wuv_h o_h[:rank]) sigmoid(gate)."""
+    n = out.shape[0]
+    _need(o.dtype == w_uv.dtype == out.dtype and o.is_contiguous() and o.numel() == n * H * hd
+          and w_uv.is_contiguous() and w_uv.numel() == H * rank * vdim and out.is_contiguous()
+          and out.shape[1] == H * vdim, "latent_expand: shapes")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous()
+                           and gate.numel() >= n_partials * n * H * vdim), "latent_expand: gate slices")
+    _check(lib().yalm_latent_expand(_p(o), _p(w_uv), _p(gate), n_partials, n * H * vdim, _p(out),
+                                    dtype_code(out.dtype), n, H, rank, vdim, hd, _stream()), "latent_expand")
+
+
+GELU_TANH, TANH = 1, 2
+
+
+def activation_rows(z: torch.Tensor, n_partials: int, out: torch.Tensor, act: int) -> None:
+    """out = act(sum of the slices of z float32 [(s,) ...]) in out's type; act GELU_TANH or TANH."""
+    n = out.numel()
+    _need(z.dtype == torch.float32 and z.is_contiguous() and z.numel() >= n_partials * n and out.is_contiguous(),
+          "activation_rows: float32 slices in, contiguous out")
+    _check(lib().yalm_activation_rows(_p(z), n_partials, n, _p(out), dtype_code(out.dtype), n, int(act),
+                                      _stream()), "activation_rows")
 
 
 # ---- a routed feed-forward --------------------------------------------------------------

@@ -1,6 +1,7 @@
 // What follows a q/k(/v) product whose queries and keys are normed over the WHOLE projection
 // (all heads of a token at once) and rotated on a part of each head:
-//  * qk_norm_rope_store: sums the product's split-K slices, norms q and k (each over its whole
+//  * qk_norm_rope_store: sums the product's split-K slices (plus a bias per feature of the row, if
+//    the projections have one), norms q and k (each over its whole
 //    row, with a weight per feature), rotates the first `dims` features of every head -- pairs
 //    (i, i + dims/2) or neighbours (2i, 2i+1) -- by pos * freq[i] with cos and sin times `mult`,
 //    and writes q, this step's keys and values and the cache rows in the storage type.  The
@@ -22,7 +23,7 @@ namespace yalm {
 template <typename T>
 __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ qkv, int n_partials, long long partial_stride,
-    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float n_q, float n_k, float eps,
+    const float* __restrict__ bias, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float n_q, float n_k, float eps,
     const float* __restrict__ freq, int dims, int neighbours, float mult,
     const int* __restrict__ token_seq, const int* __restrict__ q_start,
     const int* __restrict__ seq_slot, const int* __restrict__ slot_pos, T* __restrict__ q_out,
@@ -50,7 +51,7 @@ __global__ void qk_norm_rope_store_kernel(
   }
   float ssq = 0.f, ssk = 0.f;
   for (int i = threadIdx.x; i < row; i += blockDim.x) {
-    const float v = sum_slices(src + i, n_partials, partial_stride);
+    const float v = sum_slices(src + i, n_partials, partial_stride) + (bias != nullptr ? bias[i] : 0.f);
     row_s[i] = v;
     if (i < nq) ssq += v * v;
     else if (i < nq + nk) ssk += v * v;
@@ -155,7 +156,7 @@ __global__ void pool_blocks_kernel(const T* __restrict__ kv_step, const T* __res
 using namespace yalm;
 
 extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long long partial_stride,
-                                       const float* q_norm, const float* k_norm, int n_q, int n_k,
+                                       const float* bias, const float* q_norm, const float* k_norm, int n_q, int n_k,
                                        float eps, const float* freq, int dims, int neighbours,
                                        float mult, const int* token_seq, const int* q_start,
                                        const int* seq_slot, const int* slot_pos, void* q_out,
@@ -186,7 +187,7 @@ extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long lo
       attr = smem;                                                                                    \
     }                                                                                                 \
     launch_pdl(qk_norm_rope_store_kernel<T>, dim3(n_tokens, parts), dim3(threads), smem, stream, qkv, \
-               n_partials, partial_stride, q_norm, k_norm, (float)n_q, (float)n_k, eps, freq, dims,   \
+               n_partials, partial_stride, bias, q_norm, k_norm, (float)n_q, (float)n_k, eps, freq, dims,   \
                neighbours, mult, token_seq, q_start, seq_slot, slot_pos, (T*)q_out, (T*)kv_step,      \
                (T*)k_cache, (T*)v_cache, H, G, hd, has_v, capacity, write_cache, page_table,          \
                pages_per_slot, n_pages);                                                              \

@@ -222,6 +222,235 @@ recurrence_scan_kernel(const float* __restrict__ act, const int* __restrict__ q_
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// A recurrence with a decay per key channel and a bonus for the current token ("wkv"), per head:
+//   o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t,   S_t = diag(w_t) S_(t-1) + k_t v_t^T,
+// S [key size, value size] in 32-bit floats per head and sequence.  Three kernels around it:
+//  * token_shift: every projection of the mixer reads its own mixture of a token's input and the
+//    previous token's, h + (h' - h) mu; the previous token of a step's first token is part of the
+//    sequence's state (zero for a new sequence);
+//  * wkv_gates: the projections' split-K slices summed into one activated row per token,
+//    (r | w | k | v) with w = exp(-exp(z + w0)), and the output gate silu(g); it also leaves the
+//    step's last input of every sequence in the state for the next step's first token;
+//  * wkv_scan: the recurrence, with recurrence_scan's layout (a lane owns RPT neighbouring rows of
+//    two value columns, tokens through a three-stage cp.async ring).
+//  * wkv_out: every head's output over its root mean square, times a weight per feature, times
+//    the gate, into the storage type.
+
+// grid (token); out [n_mix][tokens][dim] in the storage type
+template <typename T>
+__global__ void token_shift_kernel(const T* __restrict__ h, const float* __restrict__ prev,
+                                   const float* __restrict__ mu, T* __restrict__ out,
+                                   const int* __restrict__ token_seq, const int* __restrict__ q_start,
+                                   const int* __restrict__ seq_slot, int n_tokens, int dim, int n_mix) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const bool first = t == q_start[b];
+  const int slot = seq_slot[b];
+  pdl_wait();
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float hv = to_float(h[(size_t)t * dim + i]);
+    const float pv = first ? prev[(size_t)slot * dim + i] : to_float(h[(size_t)(t - 1) * dim + i]);
+    const float d = pv - hv;
+    for (int s = 0; s < n_mix; ++s)
+      out[((size_t)s * n_tokens + t) * dim + i] = from_float<T>(fmaf(d, mu[(size_t)s * dim + i], hv));
+  }
+}
+
+struct Slices {
+  const float* p;
+  int n;
+  long long stride;
+};
+
+// grid (token, part of the row); act [tokens][3 H dk + H dv] = (r | w | k | v), gate [tokens][H dv]
+template <typename T>
+__global__ void wkv_gates_kernel(Slices r, Slices k, Slices v, Slices g, Slices z,
+                                 const float* __restrict__ w0, float* __restrict__ act,
+                                 float* __restrict__ gate, const T* __restrict__ h,
+                                 float* __restrict__ prev, const int* __restrict__ token_seq,
+                                 const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                                 int n_k, int n_v, int dim) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const bool last = t == q_start[b + 1] - 1;
+  const int slot = seq_slot[b];
+  pdl_wait();
+  const int row = 3 * n_k + n_v;
+  const int e_end = min(row + n_v, (int)(blockIdx.y + 1) * 1024);
+  for (int e = blockIdx.y * 1024 + threadIdx.x; e < e_end; e += blockDim.x) {
+    if (e < n_k) {
+      act[(size_t)t * row + e] = sum_slices(r.p + (size_t)t * n_k + e, r.n, r.stride);
+    } else if (e < 2 * n_k) {
+      const int i = e - n_k;
+      const float zz = sum_slices(z.p + (size_t)t * n_k + i, z.n, z.stride) + w0[i];
+      act[(size_t)t * row + e] = expf(-expf(zz));
+    } else if (e < 3 * n_k) {
+      const int i = e - 2 * n_k;
+      act[(size_t)t * row + e] = sum_slices(k.p + (size_t)t * n_k + i, k.n, k.stride);
+    } else if (e < row) {
+      const int i = e - 3 * n_k;
+      act[(size_t)t * row + e] = sum_slices(v.p + (size_t)t * n_v + i, v.n, v.stride);
+    } else {
+      const int i = e - row;
+      const float gv = sum_slices(g.p + (size_t)t * n_v + i, g.n, g.stride);
+      gate[(size_t)t * n_v + i] = gv / (1.0f + expf(-gv));
+    }
+  }
+  if (last && blockIdx.y == 0)
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) prev[(size_t)slot * dim + i] = to_float(h[(size_t)t * dim + i]);
+}
+
+template <int RPT, int VEC>
+__global__ void __launch_bounds__(256)
+wkv_scan_kernel(const float* __restrict__ act, const float* __restrict__ bonus,
+                const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                float* __restrict__ state, float* __restrict__ out, int H, int dk, int dv) {
+  pdl_launch_dependents();
+  constexpr int DKP = 32 * RPT;                       // rows, padded
+  constexpr int PER_TOK = 3 * DKP + RC_COLS;          // r, w, k, then this block's v columns
+  extern __shared__ __align__(16) float stage[];      // [RC_STAGES][RC_TOK][PER_TOK]
+  const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * RC_COLS;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int col = c0 + w * RC_CPW;
+  const int slot = seq_slot[b];
+  const int t0 = q_start[b], t1 = q_start[b + 1];
+  const int row = 3 * H * dk + H * dv;
+  // rows beyond dk: r = k = w = 0 for ever (never copied over); their state stays zero
+  if (dk < DKP) {
+    for (int i = threadIdx.x; i < RC_STAGES * RC_TOK * PER_TOK; i += blockDim.x) stage[i] = 0.f;
+    __syncthreads();
+  }
+  const int per = 3 * dk + RC_COLS;
+  int src_off[4], dst_off[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int e = (threadIdx.x + k * 256) * VEC;
+    src_off[k] = dst_off[k] = -1;
+    if (e < 3 * dk) {
+      const int which = e / dk, i = e - which * dk;
+      src_off[k] = which * H * dk + h * dk + i;
+      dst_off[k] = which * DKP + i;
+    } else if (e < per && c0 + (e - 3 * dk) < dv) {
+      src_off[k] = 3 * H * dk + h * dv + c0 + (e - 3 * dk);
+      dst_off[k] = 3 * DKP + (e - 3 * dk);
+    }
+  }
+  float U[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    const int i = lane * RPT + r;
+    U[r] = i < dk ? bonus[h * dk + i] : 0.f;
+  }
+  pdl_wait();
+  float S[RPT][RC_CPW];
+  float* st = state + (((size_t)slot * H + h) * dk) * dv + col;
+#pragma unroll
+  for (int r = 0; r < RPT; ++r)
+#pragma unroll
+    for (int c = 0; c < RC_CPW; ++c) {
+      const int i = lane * RPT + r;
+      S[r][c] = (col + c < dv && i < dk) ? st[(size_t)i * dv + c] : 0.f;
+    }
+  const int n_groups = (t1 - t0 + RC_TOK - 1) / RC_TOK;
+  auto issue = [&](int g) {
+    if (g < n_groups) {
+      const int base = t0 + g * RC_TOK;
+      const int nt = min(RC_TOK, t1 - base);
+      float* dst = stage + (size_t)(g % RC_STAGES) * RC_TOK * PER_TOK;
+      const float* src = act + (size_t)base * row;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (src_off[k] >= 0)
+          for (int tt = 0; tt < nt; ++tt)
+            cp_async<4 * VEC>(dst + tt * PER_TOK + dst_off[k], src + (size_t)tt * row + src_off[k]);
+    }
+    cp_async_commit();
+  };
+  issue(0);
+  issue(1);
+  for (int g = 0; g < n_groups; ++g) {
+    cp_async_wait<RC_STAGES - 2>();
+    __syncthreads();                                   // stage g has landed; stage g - 1 is no longer read
+    issue(g + 2);
+    const int base = t0 + g * RC_TOK;
+    const int nt = min(RC_TOK, t1 - base);
+    const float* sg = stage + (size_t)(g % RC_STAGES) * RC_TOK * PER_TOK;
+    float o[RC_TOK][RC_CPW];
+#pragma unroll
+    for (int tt = 0; tt < RC_TOK; ++tt) {
+#pragma unroll
+      for (int c = 0; c < RC_CPW; ++c) o[tt][c] = 0.f;
+      if (tt < nt) {
+        const float* rr = sg + tt * PER_TOK + lane * RPT;
+        const float* ww = rr + DKP;
+        const float* kk = rr + 2 * DKP;
+        float vj[RC_CPW];
+#pragma unroll
+        for (int c = 0; c < RC_CPW; ++c) vj[c] = sg[tt * PER_TOK + 3 * DKP + w * RC_CPW + c];
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+          const float ri = rr[r], wi = ww[r], ki = kk[r];
+#pragma unroll
+          for (int c = 0; c < RC_CPW; ++c) {
+            const float kv = ki * vj[c];
+            o[tt][c] = fmaf(ri, fmaf(U[r], kv, S[r][c]), o[tt][c]);
+            S[r][c] = fmaf(wi, S[r][c], kv);
+          }
+        }
+      }
+    }
+    // the 32 lanes' partial sums of the group's 32 outputs, as in recurrence_scan_kernel
+    static_assert(RC_TOK * RC_CPW == 32, "one output per lane");
+    float* ov = &o[0][0];
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+      const bool upper = (lane & half) != 0;
+#pragma unroll
+      for (int i = 0; i < half; ++i) {
+        const float send = upper ? ov[i] : ov[i + half];
+        const float keep = upper ? ov[i + half] : ov[i];
+        ov[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+      }
+    }
+    {
+      const int tt = lane / RC_CPW, c = lane % RC_CPW;
+      if (tt < nt && col + c < dv) out[((size_t)(base + tt) * H + h) * dv + col + c] = ov[0];
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < RPT; ++r)
+#pragma unroll
+    for (int c = 0; c < RC_CPW; ++c) {
+      const int i = lane * RPT + r;
+      if (col + c < dv && i < dk) st[(size_t)i * dv + c] = S[r][c];
+    }
+}
+
+// a warp per (token, head)
+template <typename TO>
+__global__ void wkv_out_kernel(const float* __restrict__ o, const float* __restrict__ w,
+                               const float* __restrict__ gate, TO* __restrict__ out,
+                               long long n_heads_total, int heads, int size, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long head = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (head >= n_heads_total) return;
+  const int lane = threadIdx.x & 31;
+  const float* src = o + head * size;
+  const float* wh = w + (head % heads) * size;
+  float ss = 0.f;
+  for (int i = lane; i < size; i += 32) ss += src[i] * src[i];
+  ss = warp_sum(ss);
+  const float rs = 1.0f / sqrtf(ss / (float)size + eps);
+  for (int i = lane; i < size; i += 32)
+    out[head * size + i] = from_float<TO>(src[i] * rs * wh[i] * gate[head * size + i]);
+}
+
 }  // namespace yalm
 
 using namespace yalm;
@@ -272,6 +501,115 @@ extern "C" int yalm_gated_recurrence(const float* proj, int n_partials, long lon
   else if (rpt <= 8) YALM_REC(8);
   else YALM_REC(16);
 #undef YALM_REC
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+// out [n_mix][tokens][dim] = h + (h' - h) mu[s]; h' the previous token's row, for a step's first
+// token the sequence's prev [slots][dim] (float32)
+extern "C" int yalm_token_shift(const void* h, const float* prev, const float* mu, void* out, int dtype,
+                                const int* token_seq, const int* q_start, const int* seq_slot,
+                                int n_tokens, int dim, int n_mix, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (dim <= 0 || n_mix <= 0) return -2;
+  int threads = (dim + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  const dim3 grid(n_tokens), block(threads);
+  if (dtype == DT_F32)
+    launch_pdl(token_shift_kernel<float>, grid, block, 0, stream, (const float*)h, prev, mu, (float*)out,
+               token_seq, q_start, seq_slot, n_tokens, dim, n_mix);
+  else if (dtype == DT_BF16)
+    launch_pdl(token_shift_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)h, prev, mu,
+               (__nv_bfloat16*)out, token_seq, q_start, seq_slot, n_tokens, dim, n_mix);
+  else if (dtype == DT_F16)
+    launch_pdl(token_shift_kernel<__half>, grid, block, 0, stream, (const __half*)h, prev, mu, (__half*)out,
+               token_seq, q_start, seq_slot, n_tokens, dim, n_mix);
+  else return -3;
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+// The recurrence of a step: r, k, z [.][tokens][H dk] and v, g [.][tokens][H dv] are float32 slices
+// of the five projections (z before + w0 and exp(-exp(.))); bonus [H][dk]; act: float32 scratch
+// [tokens][3 H dk + H dv]; gate: float32 out [tokens][H dv] = silu(g); state [slots][H][dk][dv];
+// out float32 [tokens][H dv]; h [tokens][dim] (h_dtype) is the mixer's input, whose last row per
+// sequence goes to prev [slots][dim].  dk up to 256.
+extern "C" int yalm_wkv(const float* r, int nr, long long sr, const float* k, int nk, long long sk,
+                        const float* v, int nv, long long sv, const float* g, int ng, long long sg,
+                        const float* z, int nz, long long sz, const float* w0, const float* bonus,
+                        float* act, float* gate, const void* h, int h_dtype, float* prev,
+                        const int* token_seq, const int* q_start, const int* seq_slot, float* state,
+                        float* out, int n_tokens, int n_seqs, int H, int dk, int dv, int dim,
+                        cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (H <= 0 || dk <= 0 || dv <= 0 || dk > 256 || n_seqs > 65535 || H > 65535 || dim <= 0) return -2;
+  const int row = 3 * H * dk + H * dv;
+  const int parts = (row + H * dv + 1023) / 1024;
+  if (parts > 65535) return -4;
+  const Slices R = {r, nr, sr}, K = {k, nk, sk}, V = {v, nv, sv}, G = {g, ng, sg}, Z = {z, nz, sz};
+  const dim3 ggrid(n_tokens, parts), gblock(256);
+  if (h_dtype == DT_F32)
+    launch_pdl(wkv_gates_kernel<float>, ggrid, gblock, 0, stream, R, K, V, G, Z, w0, act, gate,
+               (const float*)h, prev, token_seq, q_start, seq_slot, H * dk, H * dv, dim);
+  else if (h_dtype == DT_BF16)
+    launch_pdl(wkv_gates_kernel<__nv_bfloat16>, ggrid, gblock, 0, stream, R, K, V, G, Z, w0, act, gate,
+               (const __nv_bfloat16*)h, prev, token_seq, q_start, seq_slot, H * dk, H * dv, dim);
+  else if (h_dtype == DT_F16)
+    launch_pdl(wkv_gates_kernel<__half>, ggrid, gblock, 0, stream, R, K, V, G, Z, w0, act, gate,
+               (const __half*)h, prev, token_seq, q_start, seq_slot, H * dk, H * dv, dim);
+  else return -3;
+  YALM_LAUNCH_CHECK();
+  const dim3 grid((dv + RC_COLS - 1) / RC_COLS, H, n_seqs), block(256);
+  const int rpt = (dk + 31) / 32;
+  const bool vec = dk % 4 == 0 && dv % 4 == 0 && (((uintptr_t)act) & 15) == 0;
+  if ((3 * dk + RC_COLS + (vec ? 3 : 0)) / (vec ? 4 : 1) > 4 * 256) return -2;
+#define YALM_WKV(R)                                                                                 \
+  do {                                                                                              \
+    const size_t smem = (size_t)RC_STAGES * RC_TOK * (3 * 32 * R + RC_COLS) * sizeof(float);        \
+    static bool set = false;                                                                        \
+    if (!set && smem > 48 * 1024) {                                                                 \
+      cudaError_t e = cudaFuncSetAttribute(wkv_scan_kernel<R, 4>,                                   \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e == cudaSuccess)                                                                         \
+        e = cudaFuncSetAttribute(wkv_scan_kernel<R, 1>,                                             \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+      if (e != cudaSuccess) return (int)e;                                                          \
+      set = true;                                                                                   \
+    }                                                                                               \
+    if (vec)                                                                                        \
+      launch_pdl(wkv_scan_kernel<R, 4>, grid, block, smem, stream, (const float*)act, bonus,        \
+                 q_start, seq_slot, state, out, H, dk, dv);                                         \
+    else                                                                                            \
+      launch_pdl(wkv_scan_kernel<R, 1>, grid, block, smem, stream, (const float*)act, bonus,        \
+                 q_start, seq_slot, state, out, H, dk, dv);                                         \
+  } while (0)
+  if (rpt <= 1) YALM_WKV(1);
+  else if (rpt <= 2) YALM_WKV(2);
+  else if (rpt <= 4) YALM_WKV(4);
+  else YALM_WKV(8);
+#undef YALM_WKV
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+// out [rows, heads * size] = each head's `size` values of o (float32) over their root mean square,
+// times w [heads * size], times gate [rows, heads * size] (float32)
+extern "C" int yalm_wkv_out(const float* o, const float* w, const float* gate, void* out, int out_dtype,
+                            long long rows, int heads, int size, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (heads <= 0 || size <= 0) return -2;
+  const long long total = rows * heads;
+  const long long blocks = (total + 7) / 8;
+  if (blocks > 0x7fffffffLL) return -4;
+  const dim3 grid((unsigned)blocks), block(256);
+  if (out_dtype == DT_F32)
+    launch_pdl(wkv_out_kernel<float>, grid, block, 0, stream, o, w, gate, (float*)out, total, heads, size, eps);
+  else if (out_dtype == DT_BF16)
+    launch_pdl(wkv_out_kernel<__nv_bfloat16>, grid, block, 0, stream, o, w, gate, (__nv_bfloat16*)out, total,
+               heads, size, eps);
+  else if (out_dtype == DT_F16)
+    launch_pdl(wkv_out_kernel<__half>, grid, block, 0, stream, o, w, gate, (__half*)out, total, heads, size, eps);
+  else return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }

@@ -124,6 +124,23 @@ __global__ void residual_add_kernel(float* __restrict__ x, const float* __restri
   x[i] = v + y[i];
 }
 
+// out [n] = act(sum over slices of z [S][n]) in the storage type: 1 = gelu in its tanh form,
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 2 = tanh
+template <typename T>
+__global__ void activation_rows_kernel(const float* __restrict__ z, int n_partials, long long partial_stride,
+                                       T* __restrict__ out, long long n, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = sum_slices(z + i, n_partials, partial_stride);
+    float r;
+    if (act == 1) r = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    else r = tanhf(v);
+    out[i] = from_float<T>(r);
+  }
+}
+
 }  // namespace yalm
 
 using namespace yalm;
@@ -208,6 +225,21 @@ extern "C" int yalm_residual_add(float* x, const float* y, const float* partials
   if (blocks > 0x7fffffffLL) return -4;
   launch_pdl(residual_add_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, y, partials, n_partials,
              partial_stride, n);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int yalm_activation_rows(const float* z, int n_partials, long long partial_stride, void* out,
+                                    int out_dtype, long long n, int act, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (act != 1 && act != 2) return -3;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  const dim3 grid((unsigned)blocks), block(256);
+  if (out_dtype == DT_F32) launch_pdl(activation_rows_kernel<float>, grid, block, 0, stream, z, n_partials, partial_stride, (float*)out, n, act);
+  else if (out_dtype == DT_BF16) launch_pdl(activation_rows_kernel<__nv_bfloat16>, grid, block, 0, stream, z, n_partials, partial_stride, (__nv_bfloat16*)out, n, act);
+  else if (out_dtype == DT_F16) launch_pdl(activation_rows_kernel<__half>, grid, block, 0, stream, z, n_partials, partial_stride, (__half*)out, n, act);
+  else return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }

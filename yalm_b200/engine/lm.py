@@ -54,6 +54,9 @@ class LM:
             if not hasattr(config, "with_window"):
                 raise ValueError(f"{type(config).__name__} has no window to impose")
             config = config.with_window(int(window_override))
+        if hasattr(config, "with_tensor_shapes"):
+            # sizes that a design leaves to its checkpoint's tensors
+            config = config.with_tensor_shapes({name: tuple(t.shape) for name, t in tensors.items()})
         self.config = config
         self.spec = config.to_spec()
         self.rt = Runtime(_dtype(dtype), device, gemm=gemm, attention=attention,

@@ -33,6 +33,10 @@ Options beyond that, each a parameter (all off for the Llama / Mistral decoder):
   b P + P - 1 <= pos - W), in the same softmax.  The means are formed from the rows as the
   cache holds them when a block completes, and live in a second cache with one row per block;
   the ring of the window keeps max(W, P) rows so that a completing block's rows are still there;
+* ``bias``: q, k and v have biases (``q.b``, ``k.b``, ``v.b``), added where the product's slices are summed;
+* ``keep_first`` = F (with a window W): a query also sees the positions below F, at their own
+  positions (for rotation and distance), however far back they lie.  The cache then keeps every
+  position instead of a ring of W rows;
 * ``exact_softmax``: scores, softmax weights and the weighted sum of values in 32-bit arithmetic
   (the FMA attention kernels on the 16-bit cache) instead of the tensor-core kernels, whose
   weights are rounded to 16 bits.
@@ -49,6 +53,35 @@ from ..weights import TensorNeed
 from .base import POSITIONS, make_part, register_mixer
 from . import decode_plan, linear
 from .linear import matmul_partials
+
+
+def exact_attention(rt, q, kv_step, k_cache, v_cache, batch, slot_pos, o, H, G, hd, capacity, window, pages,
+                    scale, chunk=None, pooled=None, pool=None, keep_first=None) -> None:
+    """Attention with 32-bit scores, softmax weights and weighted sum: a prompt (or a portion of
+    one) on the tensor-core kernel that carries every weight as three 16-bit terms, where that
+    kernel takes the shape; else the FMA kernel, a decode step's few queries split over their keys
+    so that the grid fills the device."""
+    n = batch.n_tokens
+    if (not batch.is_decode and rt.attention != "simt" and not keep_first
+            and ops.exact_attention_usable(rt.dtype, hd, chunk)):
+        ops.attention_exact_prefill(q, kv_step, k_cache, v_cache, batch, slot_pos, o, H, G, hd, capacity,
+                                    window, pages=pages, scale=scale, pooled=pooled)
+        return
+    bound = max(1, batch.ctx_bound)
+    span = window or chunk
+    visible = min(bound, span) if span else bound
+    if pool:
+        visible += bound // pool
+    if keep_first:
+        visible = min(bound, visible + keep_first)
+    nsplit = 1
+    if batch.is_decode:
+        blocks = n * G * -(-(H // G) // 4)
+        nsplit = max(1, min(-(-visible // 64), 2 * rt.sm_count // max(1, blocks), 64))
+    part_o = rt.buffer("attn_part_o", (n, H, nsplit, hd), torch.float32)
+    part_ml = rt.buffer("attn_part_ml", (n, H, nsplit, 2), torch.float32)
+    ops.attention(q, kv_step, k_cache, v_cache, batch, slot_pos, o, H, G, hd, capacity, window, nsplit,
+                  part_o, part_ml, pages=pages, pooled=pooled, chunk=chunk, scale=scale, keep_first=keep_first)
 
 
 @register_mixer("gqa_attention")
@@ -70,6 +103,14 @@ class GQAAttention:
         self.values_from_keys = bool(params.get("values_from_keys", False))
         self.pool: Optional[int] = params.get("pool") or None
         self.exact = bool(params.get("exact_softmax", False))
+        self.bias = bool(params.get("bias", False))
+        self.keep_first: Optional[int] = params.get("keep_first") or None
+        if self.keep_first and not self.window:
+            raise ValueError("kept first positions stay visible beside a sliding window: the mixer needs one")
+        if self.keep_first and self.pool:
+            raise ValueError("kept first positions and pooled blocks exclude each other")
+        if self.bias and params["position"].kind != "rope_partial":
+            raise ValueError("biases of q, k and v are added by the rope_partial encoding's kernel")
         if self.head_gate and self.element_gate:
             raise ValueError("a gate per head and a gate per feature exclude each other")
         if self.pool and not self.window:
@@ -98,6 +139,8 @@ class GQAAttention:
             raise ValueError(f"head size {self.hd} is not supported by the attention kernel "
                              f"(up to 256)")
         self.span = self.window or self.chunk          # the most keys a query sees, if bounded
+        if self.keep_first:
+            self.span = None                           # no ring: see ``cache_need``
         if position.kind == "rope_partial" and int(position.params.get("head_dim", self.hd)) != self.hd:
             position = type(position)(position.kind, {**position.params, "head_dim": self.hd},
                                       position.tensors)
@@ -124,6 +167,11 @@ class GQAAttention:
             needs["k.norm"] = TensorNeed((self.G * self.hd_k,), init="ones")
         if self.head_temp:
             needs["temp"] = TensorNeed((self.H,), init="ones")
+        if self.bias:
+            needs["q.b"] = TensorNeed((self.H * self.hd_k,), init="around_zero")
+            needs["k.b"] = TensorNeed((self.G * self.hd_k,), init="around_zero")
+            if not self.values_from_keys:
+                needs["v.b"] = TensorNeed((self.G * self.hd_v,), init="around_zero")
         return needs
 
     def _pad_vector(self, w: torch.Tensor, heads: int, size: int) -> torch.Tensor:
@@ -171,8 +219,16 @@ class GQAAttention:
                                            self.G * self.hd_k, float(self.qk_norm["eps"]))
         if self.values_from_keys:
             self._store_extras["has_v"] = False
+        if self.bias:
+            b = [self._pad_vector(tensors["q.b"], self.H, self.hd_k), self._pad_vector(tensors["k.b"], self.G, self.hd_k)]
+            if not self.values_from_keys:
+                b.append(self._pad_vector(tensors["v.b"], self.G, self.hd_v))
+            self._store_extras["bias"] = torch.cat(b).contiguous()
 
     def cache_need(self):
+        if self.keep_first:
+            # every position stays (the first ones are seen for ever); the mask alone bounds the keys
+            return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=None)
         if not self.pool:
             return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.span)
         # the ring keeps a completing block's rows; the pooled rows are never dropped
@@ -330,29 +386,12 @@ class GQAAttention:
                                 pages=view.pages, pool_pages=pool_view.pages)
             pooled = (pool_view.k, pool_view.v, self.pool, pool_view.capacity, pool_view.pages)
         o = rt.buffer("attn_out", (n, H * hd), rt.dtype)
-        if ((self.pool or self.exact) and not batch.is_decode and rt.attention != "simt"
-                and ops.exact_attention_usable(rt.dtype, hd, self.chunk)):
-            # a prompt (or a portion of one): tensor cores with the softmax weights kept in 32 bits
-            # (three 16-bit terms per weight); the pooled rows are key blocks in front
-            ops.attention_exact_prefill(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
-                                        view.capacity, self.window, pages=view.pages, scale=self.scale,
-                                        pooled=pooled)
-        elif self.pool or (self.exact and not batch.is_decode):
-            # 32-bit scores, weights and sums over the window's rows and the pooled rows; a decode
-            # step's few queries are split over their keys so that the grid fills the device
-            bound = max(1, batch.ctx_bound)
-            visible = min(bound, self.span) if self.span else bound
-            if self.pool:
-                visible += bound // self.pool
-            nsplit = 1
-            if batch.is_decode:
-                blocks = n * G * -(-(H // G) // 4)
-                nsplit = max(1, min(-(-visible // 64), 2 * rt.sm_count // max(1, blocks), 64))
-            part_o = rt.buffer("attn_part_o", (n, H, nsplit, hd), torch.float32)
-            part_ml = rt.buffer("attn_part_ml", (n, H, nsplit, 2), torch.float32)
-            ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
-                          view.capacity, self.window, nsplit, part_o, part_ml, pages=view.pages,
-                          pooled=pooled, **mask)
+        if self.pool or self.keep_first or (self.exact and not batch.is_decode):
+            # 32-bit scores, weights and sums over the window's rows, the pooled rows and the kept
+            # first positions
+            exact_attention(rt, q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd, view.capacity,
+                            self.window, view.pages, self.scale, chunk=self.chunk, pooled=pooled,
+                            pool=self.pool, keep_first=self.keep_first)
         elif batch.is_decode:
             # one query per sequence, every key already in the cache
             bound = max(1, batch.ctx_bound)

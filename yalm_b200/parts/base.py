@@ -212,6 +212,54 @@ class ResidualStream:
         self.branches: list = []                       # (slices [S, N, D], S, norm weight | None, factor)
         self.branch_eps = 0.0
         self.h: Optional[torch.Tensor] = None          # x in the compute type, while x is unchanged
+        # A model that keeps several residual copies per token ("hyper-connections"): float32
+        # [copies, N, D], made by ``spread``.  A sublayer's write into the copies is left here and
+        # performed by whatever reads them next (one kernel does that write and the read).
+        self.copies: Optional[torch.Tensor] = None
+        self._copy_write = None                        # (slices, S, mix, out weights, factor)
+        self._ones: Optional[torch.Tensor] = None
+
+    # -- several residual copies --------------------------------------------------------------
+    def spread(self, ones: torch.Tensor) -> None:
+        """x becomes ``len(ones)`` equal copies (``ones``: float32 ones on the device, kept for
+        ``collapse``)."""
+        self.resolve()
+        s = int(ones.numel())
+        self.copies = self.rt.buffer("residual_copies", (s,) + tuple(self.x.shape), torch.float32)
+        self.copies.copy_(self.x.unsqueeze(0).expand_as(self.copies))
+        self._ones = ones
+
+    def write_copies(self, mix: torch.Tensor, out_w: torch.Tensor, mult: float) -> None:
+        """X_j <- sum_i mix[i, j] X_i + mult out_w[j] y, y the pending product; done by the next read."""
+        if self.copies is None or not self.n_pending or self._copy_write is not None:
+            raise RuntimeError("a write into the residual copies needs copies and one pending product")
+        self._copy_write = (self.pending, self.n_pending, mix, out_w, float(mult))
+        self.pending, self.n_pending = None, 0
+
+    def read_copies(self, in_w: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float,
+                    out: torch.Tensor) -> torch.Tensor:
+        """out = norm(sum_i in_w[i] X_i) (or the sum itself, float32, without a norm weight), after
+        the write that is still due."""
+        ops.hc_step(self.copies, write=self._copy_write, read=(in_w, norm_w, eps, out))
+        self._copy_write = None
+        return out
+
+    def collapse(self) -> torch.Tensor:
+        """x <- the sum of the copies; the stream has one residual again."""
+        if self.copies is not None:
+            self.read_copies(self._ones, None, 0.0, self.x)
+            self.copies, self.h = None, None
+        return self.x
+
+    def total(self) -> torch.Tensor:
+        """The residual as one tensor [N, D] (the sum of the copies), for inspection: nothing of the
+        stream's state changes except that a due write is made."""
+        if self.copies is None:
+            return self.resolve()
+        if self._copy_write is not None:
+            ops.hc_step(self.copies, write=self._copy_write)
+            self._copy_write = None
+        return self.copies.sum(0)
 
     def as_input(self) -> torch.Tensor:
         """x itself as the input of a product: in the compute type (a copy that the last norm

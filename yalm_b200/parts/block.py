@@ -88,3 +88,47 @@ class PostNormBlock:
         finally:
             stream.hold = False
         return later
+
+
+@register_block("hyper_prenorm")
+class HyperPreNormBlock:
+    """Pre-norm sublayers over several residual copies: each sublayer reads one mixture of the
+    copies through its norm and writes its output into all of them (``hyper_rmsnorm`` owns both).
+    The feed-forward and its norm may be absent.  The stream holds the products apart (``hold``)
+    so that the write gets them as they are."""
+
+    def __init__(self, layer_spec, rt):
+        self.spec = layer_spec
+        self.mixer_norm = make_part(NORMS, layer_spec.part("mixer_norm"), rt)
+        self.mixer = make_part(MIXERS, layer_spec.part("mixer"), rt)
+        self.ffn = self.ffn_norm = None
+        if "feed_forward" in layer_spec.parts:
+            self.ffn_norm = make_part(NORMS, layer_spec.part("feed_forward_norm"), rt)
+            self.ffn = make_part(FEED_FORWARDS, layer_spec.part("feed_forward"), rt)
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not (hasattr(n, "read") and hasattr(n, "write")):
+                raise TypeError("a hyper_prenorm block needs norms that read and write the copies (hyper_rmsnorm)")
+
+    def parts(self):
+        s = self.spec
+        out = [(self.mixer_norm, s.part("mixer_norm")), (self.mixer, s.part("mixer"))]
+        if self.ffn is not None:
+            out += [(self.ffn_norm, s.part("feed_forward_norm")), (self.ffn, s.part("feed_forward"))]
+        return out
+
+    def mixers(self):
+        return {"mixer": self.mixer}
+
+    def forward(self, stream, batch, views, shared: bool = False):
+        stream.hold = True
+        try:
+            h = self.mixer_norm.read(stream)
+            later = self.mixer.forward(h, batch, stream, views["mixer"], shared=shared)
+            self.mixer_norm.write(stream)
+            if self.ffn is not None:
+                h = self.ffn_norm.read(stream)
+                self.ffn.forward(h, batch, stream)
+                self.ffn_norm.write(stream)
+        finally:
+            stream.hold = False
+        return later

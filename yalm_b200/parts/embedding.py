@@ -29,13 +29,22 @@ class Embedding:
         self.vocab = int(params["vocab_size"])
         self.size = int(params["size"])
         self.scale = float(params.get("scale") or 1.0)       # x = E[token] * scale
+        # "norm" = {"eps": e}: the looked-up row is RMS-normed with a weight ("norm") before it
+        # starts the residual stream
+        self.norm = params.get("norm") or None
         self.table = None
+        self.norm_weight = None
 
     def tensor_needs(self):
-        return {"weight": TensorNeed((self.vocab, self.size))}
+        needs = {"weight": TensorNeed((self.vocab, self.size))}
+        if self.norm:
+            needs["norm"] = TensorNeed((self.size,), init="ones")
+        return needs
 
     def bind(self, tensors) -> None:
         self.table = self.rt.matrix(tensors["weight"], share=True)
+        if self.norm:
+            self.norm_weight = self.rt.vector(tensors["norm"])
 
     def cache_need(self):
         return None
@@ -43,6 +52,8 @@ class Embedding:
     def forward(self, batch, view=None, keep_copy: bool = False):
         x = self.rt.buffer("residual", (batch.n_tokens, self.size), torch.float32)
         ops.embed(batch.tokens, self.table, x, self.rt.status, scale=self.scale)
+        if self.norm:
+            ops.sum_norm(x, 1.0, [], self.norm_weight, float(self.norm["eps"]))    # x <- n(x) w, in place
         if keep_copy:
             copy = self.rt.buffer("embedding_output", (batch.n_tokens, self.size), torch.float32)
             copy.copy_(x)

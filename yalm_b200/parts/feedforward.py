@@ -12,7 +12,7 @@ import torch
 from ..csrc import ops
 from ..weights import TensorNeed
 from .base import register_feed_forward
-from .linear import matmul_silu_mul
+from .linear import matmul_partials, matmul_silu_mul
 
 
 @register_feed_forward("swiglu")
@@ -47,6 +47,34 @@ class SwiGLU:
     def forward(self, h, batch, stream) -> None:
         act = self.rt.buffer("ffn_act", (h.shape[0], self.F), self.rt.dtype)
         matmul_silu_mul(self.rt, h, self.w_gate_up, act, self.paired)
+        stream.add_linear(act, self.w_down)
+
+
+@register_feed_forward("gelu_mlp")
+class GeluMLP:
+    """A feed-forward without a gate: x += Wdown gelu(Wup h), gelu in its tanh form,
+    0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.D = int(params["hidden_size"])
+        self.F = int(params["intermediate_size"])
+        self.w_up = self.w_down = None
+
+    def tensor_needs(self):
+        return {"up": TensorNeed((self.F, self.D)), "down": TensorNeed((self.D, self.F))}
+
+    def bind(self, tensors) -> None:
+        self.w_up = self.rt.matrix(tensors["up"])
+        self.w_down = self.rt.matrix(tensors["down"])
+
+    def flops(self, q_lens, past) -> float:
+        return 2.0 * sum(q_lens) * 2 * self.F * self.D
+
+    def forward(self, h, batch, stream) -> None:
+        z, S = matmul_partials(self.rt, h, self.w_up, "ffn_up")
+        act = self.rt.buffer("ffn_act", (h.shape[0], self.F), self.rt.dtype)
+        ops.activation_rows(z, S, act, ops.GELU_TANH)
         stream.add_linear(act, self.w_down)
 
 

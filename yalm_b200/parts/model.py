@@ -142,7 +142,7 @@ class Model:
                 n = len(contexts) * int(need.shape[-1])      # an untied table is read by rows only
             elif name == table_name:
                 n += len(contexts) * int(need.shape[-1])
-            total += n * (4 if need.init in ("ones", "around_zero") else esz)
+            total += n * (4 if need.init != "normal" else esz)
         for e in self.run_order:
             for mixer in self.layers[e.layer].mixers().values():
                 f = getattr(mixer, "cache_read_bytes", None)
@@ -215,6 +215,8 @@ class Model:
                 self.tap(i, stream)
         if n_want == 0:
             return None
+        if stream.copies is not None:
+            stream.collapse()                     # several residual copies: the output reads their sum
         h = self.final_norm(stream, rows=want_rows, n_rows=n_want, name="final_normed")
         if logits_out is None:
             logits_out = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32,

@@ -76,3 +76,46 @@ class SumRMSNorm:
         ops.sum_norm(stream.x, self.alpha, branches, self.weight, self.eps, h=h, branch_eps=beps)
         stream.pending, stream.n_pending, stream.branches = None, 0, []
         stream.h = h
+
+
+@register_norm("hyper_rmsnorm")
+class HyperRMSNorm:
+    """The read and the write of one sublayer in a model with several residual copies X_1 .. X_s
+    ("hyper-connections"), around an RMSNorm:
+
+        read:   u = sum_i in[i] X_i;   h = u / sqrt(mean(u^2) + eps) * weight
+        write:  X_j <- sum_i mix[i, j] X_i + m out[j] y    (every j from the old copies)
+
+    with y what the sublayer left pending on the stream and m = ``residual_scale``.  The write is
+    handed to the stream, which performs it together with the next read (one kernel, one pass)."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.copies = int(params["copies"])
+        self.mult = float(params.get("residual_scale", 1.0))
+        if not 1 <= self.copies <= 8:
+            raise ValueError(f"hyper_rmsnorm: {self.copies} residual copies (1 to 8)")
+        self.weight = self.w_in = self.w_out = self.w_mix = self.ones = None
+
+    def tensor_needs(self):
+        s = self.copies
+        return {"weight": TensorNeed((self.size,), init="ones"), "in": TensorNeed((s,), init="fraction"),
+                "out": TensorNeed((s,), init="ones"), "mix": TensorNeed((s, s), init="identity")}
+
+    def bind(self, tensors) -> None:
+        self.weight = self.rt.vector(tensors["weight"])
+        self.w_in = self.rt.vector(tensors["in"])
+        self.w_out = self.rt.vector(tensors["out"])
+        self.w_mix = self.rt.vector(tensors["mix"])
+        self.ones = torch.ones(self.copies, dtype=torch.float32, device=self.w_in.device)
+
+    def read(self, stream: ResidualStream, name: str = "normed") -> torch.Tensor:
+        if stream.copies is None:
+            stream.spread(self.ones)
+        out = self.rt.buffer(name, tuple(stream.x.shape), self.rt.dtype)
+        return stream.read_copies(self.w_in, self.weight, self.eps, out)
+
+    def write(self, stream: ResidualStream) -> None:
+        stream.write_copies(self.w_mix, self.w_out, self.mult)

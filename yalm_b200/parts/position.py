@@ -148,9 +148,9 @@ class PartialRope:
         self.freq = freq.to(rt.device)
 
     def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G, write_cache=True,
-                         norms=None, has_v=True) -> None:
+                         norms=None, has_v=True, bias=None) -> None:
         qn, kn, n_q, n_k, eps = norms if norms is not None else (None, None, 1, 1, 0.0)
         ops.qk_norm_rope_store(qkv, n_partials, qn, kn, n_q, n_k, eps, self.freq, self.dims,
                                self.neighbours, self.mult, batch, q_out, kv_step, view.k, view.v,
                                view.slot_pos, H, G, self.head_dim, has_v, view.capacity, write_cache,
-                               pages=view.pages)
+                               pages=view.pages, bias=bias)

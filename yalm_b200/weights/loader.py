@@ -31,8 +31,10 @@ class WeightsError(ValueError):
 @dataclass(frozen=True)
 class TensorNeed:
     """What a part declares about one of its tensors.  ``init`` is used by the
-    random-weights mode: 'normal' (N(0, std)), 'ones' (1 + N(0, jitter)) or 'around_zero'
-    (N(0, jitter), a norm weight that is stored without its 1)."""
+    random-weights mode: 'normal' (N(0, std)), 'ones' (1 + N(0, jitter)), 'around_zero'
+    (N(0, jitter), a norm weight that is stored without its 1), 'identity' (a unit matrix
+    + N(0, jitter)) or 'fraction' (1 / the last dimension + N(0, jitter): weights of a mean).
+    All but 'normal' are kept in 32 bits."""
     shape: Tuple[int, ...]
     init: str = "normal"
 

@@ -27,9 +27,12 @@ def random_tensors(needs: Dict[str, TensorNeed], seed: int, dtype: torch.dtype =
     out: Dict[str, torch.Tensor] = {}
     for name in sorted(needs):
         need = needs[name]
-        if need.init in ("ones", "around_zero"):
-            t = torch.full(need.shape, 1.0 if need.init == "ones" else 0.0, dtype=torch.float32,
-                           device=device)
+        if need.init in ("ones", "around_zero", "identity", "fraction"):
+            if need.init == "identity":           # a square mixing matrix that starts as "every one keeps its own"
+                t = torch.eye(need.shape[-1], dtype=torch.float32, device=device).expand(need.shape).clone()
+            else:
+                fill = {"ones": 1.0, "around_zero": 0.0, "fraction": 1.0 / max(1, need.shape[-1])}[need.init]
+                t = torch.full(need.shape, fill, dtype=torch.float32, device=device)
             if norm_jitter:
                 t += norm_jitter * torch.randn(need.shape, generator=gen, dtype=torch.float32,
                                                device=device)
