@@ -387,8 +387,57 @@ RUDAZEN_SIZES = {
     "w4096-pa": dict(width=4096, heads=32, kv_heads=8, head_dim=128, window=2048, pool=64, rot_dims=64,
                      rec_heads=32, rec_dim=128, rec_vdim=128, ff=11008, pattern="paap", vocab=32000),
 }
+def nekotar_config(width, wkv_heads, wkv_dim, decay_rank, lat_heads, lat_dim, rot_dim, lat_vdim, kv_rank,
+                   att_heads, att_kv, att_dim, window, keep, ff, pattern, vocab):
+    """A Nekotar configuration with layers of the sizes a served model has (random weights):
+    ``pattern`` is a string of "w" (a wkv layer), "l" (latent attention with its own latent), "s"
+    (latent attention reading the last "l" layer's latent) and "a" (windowed attention that keeps
+    the first tokens); every layer has a feed-forward, as the dense twin's layers have."""
+    mlp = {"kind": "dense", "ff": ff}
+    layers, own = [], None
+    for i, c in enumerate(pattern):
+        if c == "w":
+            layers.append({"type": "wkv", "mixer": {"heads": wkv_heads, "dim": wkv_dim, "decay_rank": decay_rank},
+                           "mlp": mlp})
+        elif c in "ls":
+            m = {"heads": lat_heads, "dim": lat_dim, "rot_dim": rot_dim, "vdim": lat_vdim, "kv_rank": kv_rank,
+                 "scale": float(lat_dim + rot_dim) ** -0.5, "rot": {"base": 1e4, "dims": rot_dim}}
+            if c == "s":
+                m["kv_from"] = own
+            else:
+                own = i
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+        else:
+            layers.append({"type": "attention", "mlp": mlp,
+                           "mixer": {"heads": att_heads, "kv_heads": att_kv, "dim": att_dim, "vdim": att_dim,
+                                     "scale": float(att_dim) ** -0.5, "mask": {"size": window, "keep_first": keep},
+                                     "rot": {"base": 1e6, "dims": att_dim}}})
+    return {"architecture": "Nekotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "streams": 4, "layers": layers}
+
+
+def nekotar_twin(width, wkv_heads, wkv_dim, decay_rank, lat_heads, lat_dim, rot_dim, lat_vdim, kv_rank,
+                 att_heads, att_kv, att_dim, window, keep, ff, pattern, vocab):
+    """The closest model the library had before: the Llama / Mistral decoder with the same width,
+    layers and feed-forward, the windowed layers' heads and a sliding window of the same size."""
+    return {"architectures": ["MistralForCausalLM"], "hidden_size": width, "intermediate_size": ff,
+            "num_hidden_layers": len(pattern), "num_attention_heads": att_heads, "num_key_value_heads": att_kv,
+            "head_dim": att_dim, "vocab_size": vocab, "max_position_embeddings": 32768, "rms_norm_eps": 1e-6,
+            "rope_theta": 10000.0, "sliding_window": window, "tie_word_embeddings": False,
+            "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2}
+
+
+NEKOTAR_SIZES = {
+    "w2048-wwla": dict(width=2048, wkv_heads=32, wkv_dim=64, decay_rank=64, lat_heads=16, lat_dim=64, rot_dim=32,
+                       lat_vdim=64, kv_rank=96, att_heads=16, att_kv=4, att_dim=128, window=1024, keep=64,
+                       ff=5632, pattern="wwlawwsa", vocab=32000),
+    "w4096-wla": dict(width=4096, wkv_heads=64, wkv_dim=64, decay_rank=128, lat_heads=32, lat_dim=128, rot_dim=64,
+                      lat_vdim=128, kv_rank=192, att_heads=32, att_kv=8, att_dim=128, window=2048, keep=128,
+                      ff=11008, pattern="wlaw", vocab=32000),
+}
 DESIGNS = {"golulix": (DESIGN_SIZES, golulix_config, dense_twin),
-           "rudazen": (RUDAZEN_SIZES, rudazen_config, rudazen_twin)}
+           "rudazen": (RUDAZEN_SIZES, rudazen_config, rudazen_twin),
+           "nekotar": (NEKOTAR_SIZES, nekotar_config, nekotar_twin)}
 
 
 def compare_designs(args, pk):
@@ -532,7 +581,7 @@ def main():
                          "beside the dense decoder at equal sizes (random weights, a few layers)")
     ap.add_argument("--design", default="golulix", choices=sorted(DESIGNS),
                     help="with --compare-designs: which design runs beside the dense decoder")
-    ap.add_argument("--design-size", default=None, choices=sorted(set(DESIGN_SIZES) | set(RUDAZEN_SIZES)),
+    ap.add_argument("--design-size", default=None, choices=sorted(set(DESIGN_SIZES) | set(RUDAZEN_SIZES) | set(NEKOTAR_SIZES)),
                     help="with --compare-designs: one of the design's sizes instead of all")
     args = ap.parse_args()
 

@@ -75,6 +75,13 @@ def plain_softmax_mix(q, k, v, scale: float, visible: torch.Tensor) -> torch.Ten
     return torch.einsum("hij,jhd->ihd", torch.softmax(s, dim=-1), v)
 
 
+def plain_kept_window_mask(T: int, size: int, keep_first: int) -> torch.Tensor:
+    """[T, T] bool: query i sees key j <= i inside the last ``size`` positions or among the first ``keep_first``."""
+    pos = torch.arange(T)
+    i, j = pos[:, None], pos[None, :]
+    return (j <= i) & ((i - j < size) | (j < keep_first))
+
+
 # ----------------------------------------------------------------------------- mixers
 def plain_window_attention(w, p: str, m: dict, h: torch.Tensor) -> torch.Tensor:
     T, dt = h.shape[0], h.dtype
@@ -88,11 +95,9 @@ def plain_window_attention(w, p: str, m: dict, h: torch.Tensor) -> torch.Tensor:
         k = plain_rotate(k, pos, float(rot["base"]), int(rot["dims"]), neighbours=False)
     k = k.repeat_interleave(H // G, dim=1)
     v = v.repeat_interleave(H // G, dim=1)
-    i, j = pos[:, None], pos[None, :]
-    visible = j <= i
     mask = m.get("mask")
-    if mask:
-        visible = visible & ((i - j < int(mask["size"])) | (j < int(mask.get("keep_first", 0))))
+    visible = plain_kept_window_mask(T, int(mask["size"]), int(mask.get("keep_first", 0))) if mask \
+        else pos[None, :] <= pos[:, None]
     o = plain_softmax_mix(q, k, v, float(m["scale"]), visible).reshape(T, H * dv)
     o = o * torch.sigmoid(h @ w[f"{p}.g"].to(dt).T)
     return o @ w[f"{p}.o"].to(dt).T

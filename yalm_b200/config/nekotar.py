@@ -229,6 +229,7 @@ class NekotarConfig:
             final_norm=PartSpec("rmsnorm", {"size": D, "eps": self.eps}, {"weight": "final.norm"}),
             head=PartSpec("linear_head", {"vocab_size": self.vocab, "size": D, "tied": False},
                           {"weight": "head"}),
+            overlapped_launches=False,
         )
         spec.validate()
         return spec

@@ -75,6 +75,9 @@ class ModelSpec:
     # the context when the caller names none (a design without a largest position
     # has no natural one); None: max_positions
     default_context: Optional[int] = None
+    # False: each kernel of a step starts only when the one before it has ended (no
+    # programmatic dependent launch); for a design whose kernel chain is not proven under it
+    overlapped_launches: bool = True
 
     def validate(self) -> None:
         if not self.layers:

@@ -17,6 +17,7 @@ import torch
 from ..cache import Cache, CacheNeed
 from ..cache.storage import normalise_needs
 from ..config import ModelSpec
+from ..csrc import ops
 from ..weights import TensorNeed, check_tensors
 from .base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, ResidualStream, Runtime, make_part)
 
@@ -186,6 +187,16 @@ class Model:
         """Runs the batch's tokens through every run entry, writing the cache;
         returns float32 logits [n_want, vocab] (None when nothing is wanted).
         Positions are NOT advanced here (the step function does that)."""
+        if not self.spec.overlapped_launches:
+            ops.set_pdl(False)
+            try:
+                return self._forward(batch, cache, want_rows, n_want, logits_out)
+            finally:
+                ops.set_pdl(True)
+        return self._forward(batch, cache, want_rows, n_want, logits_out)
+
+    def _forward(self, batch, cache: Cache, want_rows: Optional[torch.Tensor], n_want: int,
+                 logits_out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         rt = self.rt
         emb_views = {n: cache.view((-1, "embedding", n)) for n in normalise_needs(
             getattr(self.embedding, "cache_need", lambda: None)())}
