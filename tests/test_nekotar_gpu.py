@@ -265,6 +265,62 @@ def test_window_with_kept_first_positions(ops, window, keep, dt):
         assert not bad.numel(), f"sequence {s}: first wrong position {int(bad[0])} (window {window}, kept {keep})"
 
 
+@pytest.mark.parametrize("window, keep", [(50, 70), (64, 1), (130, 64), (7, 200)])
+@pytest.mark.parametrize("hd", [32, 64, 128])
+def test_prompt_kernel_with_kept_first_positions(ops, window, keep, hd):
+    """The tensor-core kernel for prompts: kept positions in blocks of their own before the window's
+    blocks, from the cache (a later portion) or from the step's rows, also more kept positions than
+    a key block holds and a window that reaches back into them."""
+    g = torch.Generator().manual_seed(window * 7 + keep + hd)
+    dt, H, G, cap = torch.bfloat16, 4, 2, 448
+    seqs = {0: 430, 2: 201}
+    data = {s: (torch.randn(n, H, hd, generator=g).to(dt), torch.randn(n, G, hd, generator=g).to(dt),
+                torch.randn(n, G, hd, generator=g).to(dt)) for s, n in seqs.items()}
+    kc, vc = torch.zeros(3, G, cap, hd, dtype=dt, device=DEV), torch.zeros(3, G, cap, hd, dtype=dt, device=DEV)
+    slot_pos = torch.zeros(3, dtype=torch.int32, device=DEV)
+    got, at = {s: [] for s in seqs}, {s: 0 for s in seqs}
+    for sizes in ({0: 71, 2: 2}, {0: 2, 2: 199}, {0: 193}, {0: 164}):
+        slots = list(sizes)
+        b = B([sizes[s] for s in slots], slots)
+        q = torch.cat([data[s][0][at[s]:at[s] + sizes[s]] for s in slots]).reshape(b.n_tokens, H * hd).to(DEV)
+        kv = torch.stack([torch.cat([data[s][1][at[s]:at[s] + sizes[s]] for s in slots]),
+                          torch.cat([data[s][2][at[s]:at[s] + sizes[s]] for s in slots])], 1).contiguous().to(DEV)
+        ops.cache_write(kv, b, kc, vc, slot_pos, G, hd, cap)
+        out = torch.empty(b.n_tokens, H * hd, dtype=dt, device=DEV)
+        ops.attention_exact_prefill(q, kv, kc, vc, b, slot_pos, out, H, G, hd, cap, window, scale=0.2,
+                                    keep_first=keep)
+        ops.advance(b, slot_pos)
+        qs = b.q_start.tolist()
+        for i, s in enumerate(slots):
+            got[s].append(out[qs[i]:qs[i + 1]].float().cpu())
+            at[s] += sizes[s]
+    for s, n in seqs.items():
+        q, k, v = (t.float() for t in data[s])
+        k, v = k.repeat_interleave(H // G, dim=1), v.repeat_interleave(H // G, dim=1)
+        ref = plain_softmax_mix(q, k, v, 0.2, plain_kept_window_mask(n, window, keep))
+        err = (torch.cat(got[s]).view(n, H, hd) - ref).abs().max(-1).values.max(-1).values
+        bad = (err > 2e-2 * ref.abs().max()).nonzero()
+        assert not bad.numel(), f"sequence {s}: first wrong position {int(bad[0])} (window {window}, kept {keep})"
+
+
+@pytest.mark.parametrize("M, N, K", [(300, 520, 264), (129, 64, 64), (2048, 1536, 512)])
+@pytest.mark.parametrize("act", ["gelu", "tanh"])
+def test_product_with_an_activation_on_the_way_out(ops, M, N, K, act):
+    """act(a W^T) in the two-SM product's epilogue against the same in 64-bit floats: through the
+    copy engine (rows of 16-byte multiples) and through the threads' own stores."""
+    g = torch.Generator().manual_seed(M + N)
+    a = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.2).to(torch.bfloat16)
+    z = a.double() @ w.double().T
+    ref = plain_gelu_tanh(z) if act == "gelu" else torch.tanh(z)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for dt, tol in ((torch.bfloat16, 1e-2), (torch.float32, 2e-5)):
+        out = torch.empty(M, N, dtype=dt, device=DEV)
+        ops.gemm_2sm_act(a.to(DEV), w.to(DEV), out, ops.GELU_TANH if act == "gelu" else ops.TANH, status)
+        assert int(status.item()) == 0
+        assert (out.double().cpu() - ref).abs().max().item() <= tol * ref.abs().max().item()
+
+
 # ------------------------------------------------------------------ the engine against the plain model
 def _requests(cfg, seed):
     V = cfg["vocab"]

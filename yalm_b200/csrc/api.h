@@ -139,6 +139,9 @@ int yalm_gemm_tc_glu(const void* A, const void* W, int ab_dtype, void* out, int 
 int yalm_gemm_2sm_glu(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
                       int N, int K, int mode, float slope, float limit, float shift, int* status,
                       cudaStream_t stream);
+// yalm_gemm_2sm in mode 0 with out = act(A W^T): act 1 the tanh form of GELU, 2 tanh.
+int yalm_gemm_2sm_act(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
+                      int N, int K, int act, int* status, cudaStream_t stream);
 // 0 if the driver's tensor-map encoder was found (host-side set-up of yalm_gemm_tc).
 int yalm_gemm_tc_available(void);
 
@@ -198,14 +201,16 @@ int yalm_attention_keep_first(const void* q, const void* kv_step, const void* k_
 
 // Prefill attention with 32-bit softmax weights on tensor cores (attention_exact.cu; dtype 1 or 2,
 // head size 32, 64 or 128, window >= 0): S = Q K^T by mma.sync, softmax in 32 bits, P split into
-// three 16-bit terms for three P V products.  pool > 0: the pooled rows take part.
+// three 16-bit terms for three P V products.  pool > 0: the pooled rows take part.  keep_first > 0
+// (with a window, without a pool): the first keep_first positions stay visible beside the window.
 int yalm_attention_exact_prefill(const void* q, const void* kv_step, const void* k_cache,
                                  const void* v_cache, const int* q_start, const int* seq_slot,
                                  const int* slot_pos, void* out, int dtype, int n_seqs, int max_q_len,
                                  int H, int G, int hd, int capacity, int window, float scale,
                                  const int* page_table, int pages_per_slot, int n_pages,
                                  const void* pool_k, const void* pool_v, int pool, int pool_capacity,
-                                 const int* pool_table, int pool_pps, int pool_pages, cudaStream_t stream);
+                                 const int* pool_table, int pool_pps, int pool_pages, int keep_first,
+                                 cudaStream_t stream);
 
 // ---- qk_store.cu: after a q/k(/v) product with whole-projection norms and partial rotation ----
 // qkv: float32 slices [n_partials][tokens][(H + G (+ G)) hd] = (q | k | v, v only with has_v).

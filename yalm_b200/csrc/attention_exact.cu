@@ -24,6 +24,7 @@ struct ExactPool {
   const void* v;
   const int* table;
   int pps, n_pages, capacity, pool;
+  int keep;                // > 0: beside its window a query also sees the positions below `keep`
 };
 __device__ __forceinline__ int exact_pooled_visible(int pos, int window, int pool) {
   if (pool <= 0 || window <= 0) return 0;
@@ -115,13 +116,24 @@ attn_exact_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kv_step
   const int j_lo = first_visible(p_first, window);
   const int n_pool_blocks = (nb_max + EX_BK - 1) / EX_BK;
   const int n_tok_blocks = (p_last - j_lo + EX_BK) / EX_BK;
-  const int n_blocks = n_pool_blocks + n_tok_blocks;
+  // kept first positions that lie before the tile's earliest window: blocks of their own, at their
+  // own positions, visible to every row of the tile (those inside a window come with the window)
+  const int n_front = pl.keep > 0 ? min(pl.keep, j_lo) : 0;
+  const int n_head_blocks = n_pool_blocks + (n_front + EX_BK - 1) / EX_BK;
+  const int n_blocks = n_head_blocks + n_tok_blocks;
+  auto block_base = [&](int kb) {
+    return kb < n_pool_blocks ? kb * EX_BK
+         : kb < n_head_blocks ? (kb - n_pool_blocks) * EX_BK : j_lo + (kb - n_head_blocks) * EX_BK;
+  };
+  auto block_limit = [&](int kb) {
+    return kb < n_pool_blocks ? nb_max : kb < n_head_blocks ? n_front : p_last + 1;
+  };
   // a key block's rows into buffer (kb & 1): this thread copies half a row of K and of V in
   // 16-byte cp.async pieces; rows beyond the range are filled with zeros (source size 0)
   auto issue = [&](int kb) {
     const bool pooled = kb < n_pool_blocks;
-    const int base = pooled ? kb * EX_BK : j_lo + (kb - n_pool_blocks) * EX_BK;
-    const int limit = pooled ? nb_max : p_last + 1;
+    const int base = block_base(kb);
+    const int limit = block_limit(kb);
     const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
     const int key = base + row;
     const T *kp = q, *vp = q;                          // any valid address when nothing is read
@@ -155,8 +167,8 @@ attn_exact_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kv_step
   if (n_blocks > 0) issue(0);
   for (int kb = 0; kb < n_blocks; ++kb) {
     const bool pooled = kb < n_pool_blocks;
-    const int base = pooled ? kb * EX_BK : j_lo + (kb - n_pool_blocks) * EX_BK;
-    const int limit = pooled ? nb_max : p_last + 1;
+    const int base = block_base(kb);
+    const int limit = block_limit(kb);
     if (kb + 1 < n_blocks) {                           // the next block's copies run under this block's products
       issue(kb + 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -195,7 +207,8 @@ attn_exact_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kv_step
         const int pos = rr ? pos1 : pos0;
         const bool row_ok = (rr ? r1 : r0) < ql;
         const bool see = row_ok && key < limit &&
-                         (pooled ? key < (rr ? vis1 : vis0) : (key <= pos && key >= (rr ? lo1 : lo0)));
+                         (pooled ? key < (rr ? vis1 : vis0)
+                                 : (key <= pos && (key >= (rr ? lo1 : lo0) || key < pl.keep)));
         const float v = see ? s[nt][e] * scale_log2 : -INFINITY;
         s[nt][e] = v;
         mx[rr] = fmaxf(mx[rr], v);
@@ -264,7 +277,9 @@ using namespace yalm;
 
 // Prefill attention with 32-bit softmax weights on tensor cores (dtype 1 or 2; head size 32, 64
 // or 128; window >= 0).  Keys of this step come from kv_step, earlier ones from the cache ring;
-// with pool > 0 the pooled rows of yalm_attention_pooled take part.  q, out [tokens, H, hd].
+// with pool > 0 the pooled rows of yalm_attention_pooled take part; with keep_first > 0 (and a
+// window, no pool) the first keep_first positions stay visible beside the window, and the cache
+// holds every position.  q, out [tokens, H, hd].
 extern "C" int yalm_attention_exact_prefill(const void* q, const void* kv_step, const void* k_cache,
                                             const void* v_cache, const int* q_start, const int* seq_slot,
                                             const int* slot_pos, void* out, int dtype, int n_seqs,
@@ -272,13 +287,14 @@ extern "C" int yalm_attention_exact_prefill(const void* q, const void* kv_step, 
                                             float scale, const int* page_table, int pages_per_slot,
                                             int n_pages, const void* pool_k, const void* pool_v, int pool,
                                             int pool_capacity, const int* pool_table, int pool_pps,
-                                            int pool_pages, cudaStream_t stream) {
+                                            int pool_pages, int keep_first, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
   if (hd != 32 && hd != 64 && hd != 128) return -2;
   if (G <= 0 || H % G != 0 || window < 0 || (pool > 0 && window <= 0)) return -3;
+  if (keep_first < 0 || (keep_first > 0 && (window <= 0 || pool > 0))) return -3;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (H > 65535 || n_seqs > 65535) return -4;
-  const ExactPool pl = {pool_k, pool_v, pool_table, pool_pps, pool_pages, pool_capacity, pool > 0 ? pool : 0};
+  const ExactPool pl = {pool_k, pool_v, pool_table, pool_pps, pool_pages, pool_capacity, pool > 0 ? pool : 0, keep_first};
   const dim3 grid(H, (max_q_len + EX_BQ - 1) / EX_BQ, n_seqs), block(128);
   if (grid.y > 65535) return -4;
   const size_t smem = (size_t)2 * 2 * EX_BK * (hd + 8) * 2;

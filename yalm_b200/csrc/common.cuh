@@ -81,7 +81,15 @@ __device__ __forceinline__ void silu_pairs_of_chunk(const float* v, int lane, fl
 // (no clamps when limit <= 0).  For results that are rounded to a 16-bit type: 2^x and the
 // division are the special-function unit's approximations, as in silu_times_fast, whose bits it
 // gives for the SiLU case.
-struct GluParams { float slope, limit, shift; };
+// `store_act` is for the ungated stores instead: out = act(product), 1 the tanh form of GELU, 2 tanh
+// (the two-SM product's mode 0).
+struct GluParams { float slope, limit, shift; int store_act; };
+
+__device__ __forceinline__ float store_activation(float v, int act) {
+  if (act == 1) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  if (act == 2) return tanhf(v);
+  return v;
+}
 
 __device__ __forceinline__ float glu_clamped_fast(float g, float u, const GluParams& p) {
   if (p.limit > 0.f) {

@@ -116,7 +116,7 @@ template <int BT, int NACC> struct TcCfg {
 // 4: silu(gate)*up with gate and up rows interleaved in groups of 16 (out is [M, N/2]).
 // `glu` generalises the activation of modes 2 and 4 (see GluParams; SiLU is {1, 0, 0}).
 // The activation of the call that is being launched: SiLU unless an entry point set another.
-static thread_local GluParams g_glu = {1.f, 0.f, 0.f};
+static thread_local GluParams g_glu = {1.f, 0.f, 0.f, 0};
 
 template <int BT, int NACC>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -998,6 +998,10 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int c0 = 0; c0 < ncols; c0 += 16, ++stage_it) {
           float v[16];
           tmem_ld16(taddr + c0, v);
+          if (mode == 0 && glu.store_act != 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = store_activation(v[j], glu.store_act);
+          }
           const uint32_t st = smem_u32(epi_smem) + (uint32_t)((stage_it & 1) * 16 * TC_BM * esz);
           // the copy that read this buffer two chunks ago has read it
           if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -1047,6 +1051,10 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           sk_store_chunk(0, DT_F32, reinterpret_cast<float*>(out) + (size_t)slice * M * n_out, v, f,
                          tok0 + c0, M, n_out);
         } else {
+          if (NACC == 1 && mode == 0 && glu.store_act != 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = store_activation(v[j], glu.store_act);
+          }
           sk_store_chunk(mode, out_dtype, out, v, f, tok0 + c0, M, n_out);
         }
       }
@@ -1230,7 +1238,7 @@ extern "C" int yalm_gemm_grouped_tc(const void* A, const void* W, int ab_dtype, 
   if (out_dtype != DT_F32 && out_dtype != ab_dtype) return -3;
   if (max_tiles > 65535 || (long long)E * N > 0x7fffffffLL) return -4;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
-  const GluParams glu = {slope, limit, shift};
+  const GluParams glu = {slope, limit, shift, 0};
 #define YALM_TCG(BT, NACC)                                                                        \
   return launch_tc_grouped<BT, NACC>(A, W, out, out_dtype, ab_dtype, rows_total, E, N, K, mode,   \
                                      first_row, tile_expert, tile_row0, n_tiles, max_tiles, glu,  \
@@ -1290,18 +1298,29 @@ extern "C" int yalm_gemm_tc_glu(const void* A, const void* W, int ab_dtype, void
                                 int M, int N, int K, int mode, float slope, float limit, float shift,
                                 int* status, cudaStream_t stream) {
   if (mode != 2 && mode != 4) return -3;
-  g_glu = {slope, limit, shift};
+  g_glu = {slope, limit, shift, 0};
   const int rc = yalm_gemm_tc(A, W, ab_dtype, out, out_dtype, M, N, K, mode, 1, status, stream);
-  g_glu = {1.f, 0.f, 0.f};
+  g_glu = {1.f, 0.f, 0.f, 0};
   return rc;
 }
 extern "C" int yalm_gemm_2sm_glu(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
                                  int M, int N, int K, int mode, float slope, float limit, float shift,
                                  int* status, cudaStream_t stream) {
   if (mode != 2 && mode != 4) return -3;
-  g_glu = {slope, limit, shift};
+  g_glu = {slope, limit, shift, 0};
   const int rc = yalm_gemm_2sm(A, W, ab_dtype, out, out_dtype, M, N, K, mode, 1, status, stream);
-  g_glu = {1.f, 0.f, 0.f};
+  g_glu = {1.f, 0.f, 0.f, 0};
+  return rc;
+}
+
+// yalm_gemm_2sm in mode 0 with an activation on the way out: out = act(A W^T), act 1 the tanh form
+// of GELU, 2 tanh, applied to the 32-bit sums before they are rounded to out's type.
+extern "C" int yalm_gemm_2sm_act(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
+                                 int M, int N, int K, int act, int* status, cudaStream_t stream) {
+  if (act != 1 && act != 2) return -3;
+  g_glu = {1.f, 0.f, 0.f, act};
+  const int rc = yalm_gemm_2sm(A, W, ab_dtype, out, out_dtype, M, N, K, 0, 1, status, stream);
+  g_glu = {1.f, 0.f, 0.f, 0};
   return rc;
 }
 

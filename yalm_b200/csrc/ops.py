@@ -91,13 +91,14 @@ _SIGNATURES = {
     "yalm_glu_clamp": [_vp, _i, _ll, _vp, _i, _ll, _i, _f, _f, _f, _i, _vp],
     "yalm_gemm_tc_glu": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _vp],
     "yalm_gemm_2sm_glu": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _vp],
+    "yalm_gemm_2sm_act": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_grouped_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _f,
                              _f, _vp, _vp],
     "yalm_routed_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "yalm_attention_pooled": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                               _i, _i, _f, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_exact_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
-                                     _f, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
+                                     _f, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _i, _vp],
     "yalm_qk_norm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _vp, _i, _i, _f, _vp, _vp, _vp, _vp,
                                 _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_pool_blocks": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i,
@@ -594,6 +595,18 @@ def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
                                N, K, mode, splits, _p(status), _stream()), "gemm_2sm")
 
 
+def gemm_2sm_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int, status: torch.Tensor) -> None:
+    """out = act(a @ w.T) in one launch of the two-SM product: the activation (GELU_TANH or TANH)
+    is applied to the 32-bit sums in the epilogue, before they are rounded to out's type."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a.dtype == w.dtype and a.dtype in HALF_TYPES and w.shape[1] == K and a.is_contiguous()
+          and w.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (M, N)
+          and out.dtype in (a.dtype, torch.float32), "gemm_2sm_act: operands")
+    _check(lib().yalm_gemm_2sm_act(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M, N, K,
+                                   int(act), _p(status), _stream()), "gemm_2sm_act")
+
+
 def gemm_2sm_token_tile(M: int, N: int, splits: int = 1) -> int:
     """The token tile (256 or 240) that gemm_2sm takes for these sizes."""
     return lib().yalm_gemm_2sm_token_tile(M, N, splits)
@@ -720,9 +733,9 @@ def exact_attention_usable(dtype: torch.dtype, hd: int, chunk: Optional[int] = N
 def attention_exact_prefill(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
                             v_cache: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor,
                             H: int, G: int, hd: int, capacity: int, window: Optional[int], pages=None,
-                            scale: Optional[float] = None, pooled=None) -> None:
+                            scale: Optional[float] = None, pooled=None, keep_first: Optional[int] = None) -> None:
     """Prefill attention on tensor cores with the weights split into three 16-bit terms (no
-    rounding of the softmax weights); ``pooled`` as in ``attention``."""
+    rounding of the softmax weights); ``pooled`` and ``keep_first`` as in ``attention``."""
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.dtype in HALF_TYPES
           and q.is_contiguous() and kv_step.is_contiguous() and out.is_contiguous(),
@@ -734,10 +747,13 @@ def attention_exact_prefill(q: torch.Tensor, kv_step: torch.Tensor, k_cache: tor
         _need(bool(window) and pool > 0 and pk.dtype == pv.dtype == q.dtype,
               "attention_exact_prefill: pooled rows go with a sliding window")
         ppt, ppps, pnpg = _pages(pool_pages, pk, G, hd)
+    _need(not keep_first or (bool(window) and pooled is None),
+          "attention_exact_prefill: kept first positions go with a sliding window and no pooled rows")
     _check(lib().yalm_attention_exact_prefill(
         _p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
         _p(out), dtype_code(q.dtype), batch.n_seqs, max(batch.q_lens), H, G, hd, capacity, int(window or 0),
-        float(scale or 0.0), pt, pps, npg, _p(pk), _p(pv), int(pool), int(pcap), ppt, ppps, pnpg, _stream()),
+        float(scale or 0.0), pt, pps, npg, _p(pk), _p(pv), int(pool), int(pcap), ppt, ppps, pnpg,
+        int(keep_first or 0), _stream()),
         "attention_exact_prefill")
 
 

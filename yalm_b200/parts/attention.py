@@ -62,10 +62,10 @@ def exact_attention(rt, q, kv_step, k_cache, v_cache, batch, slot_pos, o, H, G, 
     kernel takes the shape; else the FMA kernel, a decode step's few queries split over their keys
     so that the grid fills the device."""
     n = batch.n_tokens
-    if (not batch.is_decode and rt.attention != "simt" and not keep_first
+    if (not batch.is_decode and rt.attention != "simt"
             and ops.exact_attention_usable(rt.dtype, hd, chunk)):
         ops.attention_exact_prefill(q, kv_step, k_cache, v_cache, batch, slot_pos, o, H, G, hd, capacity,
-                                    window, pages=pages, scale=scale, pooled=pooled)
+                                    window, pages=pages, scale=scale, pooled=pooled, keep_first=keep_first)
         return
     bound = max(1, batch.ctx_bound)
     span = window or chunk

@@ -12,7 +12,7 @@ import torch
 from ..csrc import ops
 from ..weights import TensorNeed
 from .base import register_feed_forward
-from .linear import matmul_partials, matmul_silu_mul
+from .linear import matmul_act, matmul_partials, matmul_silu_mul
 
 
 @register_feed_forward("swiglu")
@@ -72,9 +72,8 @@ class GeluMLP:
         return 2.0 * sum(q_lens) * 2 * self.F * self.D
 
     def forward(self, h, batch, stream) -> None:
-        z, S = matmul_partials(self.rt, h, self.w_up, "ffn_up")
         act = self.rt.buffer("ffn_act", (h.shape[0], self.F), self.rt.dtype)
-        ops.activation_rows(z, S, act, ops.GELU_TANH)
+        matmul_act(self.rt, h, self.w_up, act, ops.GELU_TANH, "ffn_up")
         stream.add_linear(act, self.w_down)
 
 

@@ -126,6 +126,17 @@ def matmul_partials(rt, a: torch.Tensor, w: torch.Tensor, name: str) -> Tuple[to
     return buf, 1
 
 
+def matmul_act(rt, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int, name: str) -> None:
+    """out = act(a @ w.T), act one of ops.GELU_TANH / ops.TANH, applied to the 32-bit sums: many
+    tokens in the two-SM product's epilogue (one launch, no 32-bit product in memory), few as
+    slices of K and one pass that sums and activates them."""
+    if _use_tc(rt, a, w) and a.shape[0] > MANY_TOKENS:
+        ops.gemm_2sm_act(a, w, out, act, rt.status)
+        return
+    z, S = matmul_partials(rt, a, w, name)
+    ops.activation_rows(z, S, out, act)
+
+
 def _many_tokens(rt, a, w, out, mode, glu=None) -> None:
     """Many tokens: the two-SM kernel (pairs of blocks share a 256-feature tile, so each
     byte from L2 feeds 1.5 times the arithmetic; measured 1.03-1.31 PFLOP/s at 2,048

@@ -21,7 +21,7 @@ from ..cache import CacheNeed
 from ..csrc import ops
 from ..weights import TensorNeed
 from .base import register_mixer
-from .linear import matmul_partials
+from .linear import matmul_act, matmul_partials
 
 MIXES = ("r", "k", "v", "g", "w")
 
@@ -79,9 +79,8 @@ class WkvTimeMix:
         mixed = rt.buffer("wkv_mixed", (len(MIXES), n, self.D), rt.dtype)
         ops.token_shift(h, prev, self.mu, mixed, batch)
         proj = {s: matmul_partials(rt, mixed[i], self.w[s], f"wkv_{s}") for i, s in enumerate(MIXES[:4])}
-        low, S = matmul_partials(rt, mixed[4], self.w["w1"], "wkv_w1")
         low_act = rt.buffer("wkv_w1_act", (n, self.rank), rt.dtype)
-        ops.activation_rows(low, S, low_act, ops.TANH)
+        matmul_act(rt, mixed[4], self.w["w1"], low_act, ops.TANH, "wkv_w1")
         z = matmul_partials(rt, low_act, self.w["w2"], "wkv_w2")
         act = rt.buffer("wkv_act", (n, 3 * H * dk + H * dv), torch.float32)
         gate = rt.buffer("wkv_gate", (n, H * dv), torch.float32)
