@@ -239,7 +239,48 @@ recurrence_scan_kernel(const float* __restrict__ act, const int* __restrict__ q_
 //    the gate, into the storage type.
 
 // grid (token); out [n_mix][tokens][dim] in the storage type
+// four neighbouring elements of a row as floats, and back (16-byte or 8-byte accesses)
 template <typename T>
+__device__ __forceinline__ void load_four(const T* __restrict__ p, float* f) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) f[j] = to_float(e[j]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store_four(T* __restrict__ p, const float* f) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  } else {
+    uint2 u;
+    T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) e[j] = from_float<T>(f[j]);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+}
+// sum_slices for four neighbouring elements (16-byte loads; each element's sum in the same order)
+__device__ __forceinline__ void sum_slices_four(const float* __restrict__ p, int n_partials,
+                                                long long partial_stride, float* v) {
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  for (int s0 = 0; s0 < n_partials; s0 += 4) {
+    float4 t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      t[j] = s0 + j < n_partials ? *reinterpret_cast<const float4*>(p + (size_t)(s0 + j) * partial_stride)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { v[0] += t[j].x; v[1] += t[j].y; v[2] += t[j].z; v[3] += t[j].w; }
+  }
+}
+
+// VEC: dim is a multiple of four, a thread takes four neighbouring features
+template <typename T, bool VEC>
 __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restrict__ prev,
                                    const float* __restrict__ mu, T* __restrict__ out,
                                    const int* __restrict__ token_seq, const int* __restrict__ q_start,
@@ -250,6 +291,20 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restr
   const bool first = t == q_start[b];
   const int slot = seq_slot[b];
   pdl_wait();
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+      float hv[4], pv[4], m[4], o[4];
+      load_four(h + (size_t)t * dim + i, hv);
+      if (first) load_four(prev + (size_t)slot * dim + i, pv);
+      else load_four(h + (size_t)(t - 1) * dim + i, pv);
+      for (int s = 0; s < n_mix; ++s) {
+        load_four(mu + (size_t)s * dim + i, m);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = fmaf(pv[j] - hv[j], m[j], hv[j]);
+        store_four(out + ((size_t)s * n_tokens + t) * dim + i, o);
+      }
+    }
+  } else
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
     const float hv = to_float(h[(size_t)t * dim + i]);
     const float pv = first ? prev[(size_t)slot * dim + i] : to_float(h[(size_t)(t - 1) * dim + i]);
@@ -266,7 +321,9 @@ struct Slices {
 };
 
 // grid (token, part of the row); act [tokens][3 H dk + H dv] = (r | w | k | v), gate [tokens][H dv]
-template <typename T>
+// VEC: H dk and H dv are multiples of four (and the slices 16-byte aligned), a thread takes four
+// neighbouring elements of one of the five parts
+template <typename T, bool VEC>
 __global__ void wkv_gates_kernel(Slices r, Slices k, Slices v, Slices g, Slices z,
                                  const float* __restrict__ w0, float* __restrict__ act,
                                  float* __restrict__ gate, const T* __restrict__ h,
@@ -281,6 +338,34 @@ __global__ void wkv_gates_kernel(Slices r, Slices k, Slices v, Slices g, Slices 
   pdl_wait();
   const int row = 3 * n_k + n_v;
   const int e_end = min(row + n_v, (int)(blockIdx.y + 1) * 1024);
+  if (VEC) {
+    for (int e = blockIdx.y * 1024 + threadIdx.x * 4; e < e_end; e += blockDim.x * 4) {
+      float a[4];
+      if (e >= row) {
+        const int i = e - row;
+        sum_slices_four(g.p + (size_t)t * n_v + i, g.n, g.stride, a);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = a[j] / (1.0f + expf(-a[j]));
+        store_four(gate + (size_t)t * n_v + i, a);
+        continue;
+      }
+      if (e < n_k) {
+        sum_slices_four(r.p + (size_t)t * n_k + e, r.n, r.stride, a);
+      } else if (e < 2 * n_k) {
+        const int i = e - n_k;
+        float w[4];
+        sum_slices_four(z.p + (size_t)t * n_k + i, z.n, z.stride, a);
+        load_four(w0 + i, w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = expf(-expf(a[j] + w[j]));
+      } else if (e < 3 * n_k) {
+        sum_slices_four(k.p + (size_t)t * n_k + (e - 2 * n_k), k.n, k.stride, a);
+      } else {
+        sum_slices_four(v.p + (size_t)t * n_v + (e - 3 * n_k), v.n, v.stride, a);
+      }
+      store_four(act + (size_t)t * row + e, a);
+    }
+  } else
   for (int e = blockIdx.y * 1024 + threadIdx.x; e < e_end; e += blockDim.x) {
     if (e < n_k) {
       act[(size_t)t * row + e] = sum_slices(r.p + (size_t)t * n_k + e, r.n, r.stride);
@@ -512,19 +597,18 @@ extern "C" int yalm_token_shift(const void* h, const float* prev, const float* m
                                 int n_tokens, int dim, int n_mix, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (dim <= 0 || n_mix <= 0) return -2;
-  int threads = (dim + 31) / 32 * 32;
+  const bool vec = dim % 4 == 0 && ((((uintptr_t)h) | ((uintptr_t)prev) | ((uintptr_t)mu) | ((uintptr_t)out)) & 15) == 0;
+  int threads = ((vec ? dim / 4 : dim) + 31) / 32 * 32;
   if (threads > 512) threads = 512;
   const dim3 grid(n_tokens), block(threads);
-  if (dtype == DT_F32)
-    launch_pdl(token_shift_kernel<float>, grid, block, 0, stream, (const float*)h, prev, mu, (float*)out,
-               token_seq, q_start, seq_slot, n_tokens, dim, n_mix);
-  else if (dtype == DT_BF16)
-    launch_pdl(token_shift_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)h, prev, mu,
-               (__nv_bfloat16*)out, token_seq, q_start, seq_slot, n_tokens, dim, n_mix);
-  else if (dtype == DT_F16)
-    launch_pdl(token_shift_kernel<__half>, grid, block, 0, stream, (const __half*)h, prev, mu, (__half*)out,
-               token_seq, q_start, seq_slot, n_tokens, dim, n_mix);
+#define YALM_SHIFT(T, VEC)                                                                           \
+  launch_pdl(token_shift_kernel<T, VEC>, grid, block, 0, stream, (const T*)h, prev, mu, (T*)out,     \
+             token_seq, q_start, seq_slot, n_tokens, dim, n_mix)
+  if (dtype == DT_F32) { if (vec) YALM_SHIFT(float, true); else YALM_SHIFT(float, false); }
+  else if (dtype == DT_BF16) { if (vec) YALM_SHIFT(__nv_bfloat16, true); else YALM_SHIFT(__nv_bfloat16, false); }
+  else if (dtype == DT_F16) { if (vec) YALM_SHIFT(__half, true); else YALM_SHIFT(__half, false); }
   else return -3;
+#undef YALM_SHIFT
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -548,16 +632,17 @@ extern "C" int yalm_wkv(const float* r, int nr, long long sr, const float* k, in
   if (parts > 65535) return -4;
   const Slices R = {r, nr, sr}, K = {k, nk, sk}, V = {v, nv, sv}, G = {g, ng, sg}, Z = {z, nz, sz};
   const dim3 ggrid(n_tokens, parts), gblock(256);
-  if (h_dtype == DT_F32)
-    launch_pdl(wkv_gates_kernel<float>, ggrid, gblock, 0, stream, R, K, V, G, Z, w0, act, gate,
-               (const float*)h, prev, token_seq, q_start, seq_slot, H * dk, H * dv, dim);
-  else if (h_dtype == DT_BF16)
-    launch_pdl(wkv_gates_kernel<__nv_bfloat16>, ggrid, gblock, 0, stream, R, K, V, G, Z, w0, act, gate,
-               (const __nv_bfloat16*)h, prev, token_seq, q_start, seq_slot, H * dk, H * dv, dim);
-  else if (h_dtype == DT_F16)
-    launch_pdl(wkv_gates_kernel<__half>, ggrid, gblock, 0, stream, R, K, V, G, Z, w0, act, gate,
-               (const __half*)h, prev, token_seq, q_start, seq_slot, H * dk, H * dv, dim);
+  const bool gvec = (H * dk) % 4 == 0 && (H * dv) % 4 == 0 && ((sr | sk | sv | sg | sz) & 3) == 0 &&
+                    ((((uintptr_t)r) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)g) | ((uintptr_t)z) |
+                      ((uintptr_t)w0) | ((uintptr_t)act) | ((uintptr_t)gate)) & 15) == 0;
+#define YALM_GATES(T, VEC)                                                                           \
+  launch_pdl(wkv_gates_kernel<T, VEC>, ggrid, gblock, 0, stream, R, K, V, G, Z, w0, act, gate,       \
+             (const T*)h, prev, token_seq, q_start, seq_slot, H * dk, H * dv, dim)
+  if (h_dtype == DT_F32) { if (gvec) YALM_GATES(float, true); else YALM_GATES(float, false); }
+  else if (h_dtype == DT_BF16) { if (gvec) YALM_GATES(__nv_bfloat16, true); else YALM_GATES(__nv_bfloat16, false); }
+  else if (h_dtype == DT_F16) { if (gvec) YALM_GATES(__half, true); else YALM_GATES(__half, false); }
   else return -3;
+#undef YALM_GATES
   YALM_LAUNCH_CHECK();
   const dim3 grid((dv + RC_COLS - 1) / RC_COLS, H, n_seqs), block(256);
   const int rpt = (dk + 31) / 32;
