@@ -153,7 +153,7 @@ def test_wkv_mixer_in_portions(ops, H, d, rank):
 
 
 @pytest.mark.parametrize("H, d, rd, dv, rank", [(4, 16, 8, 24, 40), (3, 32, 16, 32, 64), (5, 24, 4, 8, 20),
-                                                (2, 8, 32, 16, 96), (1, 64, 0, 64, 128)])
+                                                (2, 8, 32, 16, 96), (1, 64, 0, 64, 128), (2, 32, 64, 32, 192)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_latent_mixer_in_portions(ops, H, d, rd, dv, rank, dt):
     """The cached row [normed latent | rotated key part | 0], queries moved into the latent space,
@@ -266,7 +266,7 @@ def test_window_with_kept_first_positions(ops, window, keep, dt):
 
 
 @pytest.mark.parametrize("window, keep", [(50, 70), (64, 1), (130, 64), (7, 200)])
-@pytest.mark.parametrize("hd", [32, 64, 128])
+@pytest.mark.parametrize("hd", [32, 64, 128, 256])
 def test_prompt_kernel_with_kept_first_positions(ops, window, keep, hd):
     """The tensor-core kernel for prompts: kept positions in blocks of their own before the window's
     blocks, from the cache (a later portion) or from the step's rows, also more kept positions than

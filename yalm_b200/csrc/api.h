@@ -200,7 +200,7 @@ int yalm_attention_keep_first(const void* q, const void* kv_step, const void* k_
                               int n_pages, cudaStream_t stream);
 
 // Prefill attention with 32-bit softmax weights on tensor cores (attention_exact.cu; dtype 1 or 2,
-// head size 32, 64 or 128, window >= 0): S = Q K^T by mma.sync, softmax in 32 bits, P split into
+// head size 32, 64, 128 or 256, window >= 0): S = Q K^T by mma.sync, softmax in 32 bits, P split into
 // three 16-bit terms for three P V products.  pool > 0: the pooled rows take part.  keep_first > 0
 // (with a window, without a pool): the first keep_first positions stay visible beside the window.
 int yalm_attention_exact_prefill(const void* q, const void* kv_step, const void* k_cache,

@@ -275,8 +275,8 @@ attn_exact_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kv_step
 
 using namespace yalm;
 
-// Prefill attention with 32-bit softmax weights on tensor cores (dtype 1 or 2; head size 32, 64
-// or 128; window >= 0).  Keys of this step come from kv_step, earlier ones from the cache ring;
+// Prefill attention with 32-bit softmax weights on tensor cores (dtype 1 or 2; head size 32, 64,
+// 128 or 256; window >= 0).  Keys of this step come from kv_step, earlier ones from the cache ring;
 // with pool > 0 the pooled rows of yalm_attention_pooled take part; with keep_first > 0 (and a
 // window, no pool) the first keep_first positions stay visible beside the window, and the cache
 // holds every position.  q, out [tokens, H, hd].
@@ -289,7 +289,7 @@ extern "C" int yalm_attention_exact_prefill(const void* q, const void* kv_step, 
                                             int pool_capacity, const int* pool_table, int pool_pps,
                                             int pool_pages, int keep_first, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
-  if (hd != 32 && hd != 64 && hd != 128) return -2;
+  if (hd != 32 && hd != 64 && hd != 128 && hd != 256) return -2;
   if (G <= 0 || H % G != 0 || window < 0 || (pool > 0 && window <= 0)) return -3;
   if (keep_first < 0 || (keep_first > 0 && (window <= 0 || pool > 0))) return -3;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
@@ -315,11 +315,13 @@ extern "C" int yalm_attention_exact_prefill(const void* q, const void* kv_step, 
   if (dtype == DT_BF16) {
     if (hd == 32) YALM_EX(__nv_bfloat16, 32);
     else if (hd == 64) YALM_EX(__nv_bfloat16, 64);
-    else YALM_EX(__nv_bfloat16, 128);
+    else if (hd == 128) YALM_EX(__nv_bfloat16, 128);
+    else YALM_EX(__nv_bfloat16, 256);
   } else {
     if (hd == 32) YALM_EX(__half, 32);
     else if (hd == 64) YALM_EX(__half, 64);
-    else YALM_EX(__half, 128);
+    else if (hd == 128) YALM_EX(__half, 128);
+    else YALM_EX(__half, 256);
   }
 #undef YALM_EX
   YALM_LAUNCH_CHECK();

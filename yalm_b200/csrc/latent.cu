@@ -147,6 +147,117 @@ latent_expand_kernel(const T* __restrict__ o, const T* __restrict__ w_uv, const 
   }
 }
 
+// ---- the two per-head products for many tokens: a block of 256 threads takes 64 tokens x 64
+// columns of one head, a thread 4 x 4 of them; A and the head's matrix come through shared memory in
+// slabs of 16 of K, so that a loaded element feeds 64 multiply-adds instead of 8.  Every output is
+// the same sum, in the same order (k ascending, one fused multiply-add each), as in the kernels above.
+constexpr int HP_BM = 64, HP_BN = 64, HP_BK = 16;
+
+template <typename T, typename LoadA, typename Epi>
+__device__ __forceinline__ void head_product_tile(const T* __restrict__ B, int K, int N, int t0, int n0,
+                                                  int n_tokens, LoadA load_a, Epi epi) {
+  __shared__ __align__(16) float As[HP_BK][HP_BM + 4];     // [k][token]
+  __shared__ __align__(16) float Bs[HP_BK][HP_BN + 4];     // [k][column]
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HP_BK) {
+#pragma unroll
+    for (int r = 0; r < HP_BM * HP_BK / 256; ++r) {
+      const int i = threadIdx.x + r * 256;
+      const int tt = i / HP_BK, kk = i % HP_BK;
+      As[kk][tt] = (t0 + tt < n_tokens && k0 + kk < K) ? load_a(t0 + tt, k0 + kk) : 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < HP_BK * HP_BN / 256; ++r) {
+      const int i = threadIdx.x + r * 256;
+      const int kk = i / HP_BN, nn = i % HP_BN;
+      Bs[kk][nn] = (k0 + kk < K && n0 + nn < N) ? to_float(B[(size_t)(k0 + kk) * N + n0 + nn]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HP_BK; ++kk) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(bv[j], av[i], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = t0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (t < n_tokens && n < N) epi(t, n, acc[i][j]);
+    }
+}
+
+// grid (token tiles of 64, heads, column tiles of 64 over rank); the blocks of the first column
+// tile also write the rotated part and the zero padding
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_absorb_q_tiled_kernel(const float* __restrict__ q, int n_partials, long long partial_stride,
+                             const T* __restrict__ w_uk, const float* __restrict__ freq,
+                             const int* __restrict__ token_seq, const int* __restrict__ q_start,
+                             const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
+                             T* __restrict__ q_out, int n_tokens, int H, int dim, int rd, int rank, int hd) {
+  pdl_launch_dependents();
+  const int t0 = blockIdx.x * HP_BM, h = blockIdx.y, n0 = blockIdx.z * HP_BN;
+  const int qd = dim + rd;
+  pdl_wait();
+  head_product_tile<T>(
+      w_uk + (size_t)h * dim * rank, dim, rank, t0, n0, n_tokens,
+      [&](int t, int k) { return sum_slices(q + ((size_t)t * H + h) * qd + k, n_partials, partial_stride); },
+      [&](int t, int n, float v) { q_out[((size_t)t * H + h) * hd + n] = from_float<T>(v); });
+  if (blockIdx.z != 0) return;
+  const int tail = hd - rank;
+  for (int idx = threadIdx.x; idx < HP_BM * tail; idx += blockDim.x) {
+    const int tt = idx / tail, e = idx - tt * tail;
+    const int t = t0 + tt;
+    if (t >= n_tokens) continue;
+    float v = 0.f;
+    if (e < rd) {
+      const int b = token_seq[t];
+      const int pos = slot_pos[seq_slot[b]] + (t - q_start[b]);
+      const float ang = (float)pos * freq[e >> 1];
+      const float c = cosf(ang), s = sinf(ang);
+      const float* src = q + ((size_t)t * H + h) * qd + dim;
+      const float me = sum_slices(src + e, n_partials, partial_stride);
+      const float other = sum_slices(src + (e ^ 1), n_partials, partial_stride);
+      v = (e & 1) ? rotate_hi(other, me, c, s) : rotate_lo(me, other, c, s);
+    }
+    q_out[((size_t)t * H + h) * hd + rank + e] = from_float<T>(v);
+  }
+}
+
+// grid (token tiles of 64, heads, column tiles of 64 over vdim)
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_expand_tiled_kernel(const T* __restrict__ o, const T* __restrict__ w_uv, const float* __restrict__ gate,
+                           int n_partials, long long partial_stride, T* __restrict__ out, int n_tokens,
+                           int H, int rank, int vdim, int hd) {
+  pdl_launch_dependents();
+  const int t0 = blockIdx.x * HP_BM, h = blockIdx.y, n0 = blockIdx.z * HP_BN;
+  pdl_wait();
+  head_product_tile<T>(
+      w_uv + (size_t)h * rank * vdim, rank, vdim, t0, n0, n_tokens,
+      [&](int t, int k) { return to_float(o[((size_t)t * H + h) * hd + k]); },
+      [&](int t, int n, float acc) {
+        const size_t at = ((size_t)t * H + h) * vdim + n;
+        if (gate != nullptr) acc = acc / (1.0f + expf(-sum_slices(gate + at, n_partials, partial_stride)));
+        out[at] = from_float<T>(acc);
+      });
+}
+
+constexpr int HP_MANY = 32;        // from this many tokens on the tiled kernels run
+
 }  // namespace yalm
 
 using namespace yalm;
@@ -189,6 +300,17 @@ extern "C" int yalm_latent_absorb_q(const float* q, int n_partials, long long pa
                                     int hd, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || H > 65535 || dim <= 0 || rd < 0 || rd % 2 || rank <= 0 || hd < rank + rd) return -2;
+  if (n_tokens > HP_MANY) {
+    const dim3 grid((n_tokens + HP_BM - 1) / HP_BM, H, (rank + HP_BN - 1) / HP_BN), block(256);
+#define CALL(T)                                                                                          \
+  launch_pdl(latent_absorb_q_tiled_kernel<T>, grid, block, 0, stream, q, n_partials, partial_stride,     \
+             (const T*)w_uk, freq, token_seq, q_start, seq_slot, slot_pos, (T*)q_out, n_tokens, H, dim,  \
+             rd, rank, hd)
+    YALM_BY_TYPE(dtype, CALL);
+#undef CALL
+    YALM_LAUNCH_CHECK();
+    return 0;
+  }
   const size_t smem = (size_t)LT_TOK * (dim + rd) * sizeof(float);
   if (smem > 48 * 1024) return -2;
   const dim3 grid((n_tokens + LT_TOK - 1) / LT_TOK, H), block(256);
@@ -207,6 +329,16 @@ extern "C" int yalm_latent_expand(const void* o, const void* w_uv, const float* 
                                   int rank, int vdim, int hd, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || H > 65535 || rank <= 0 || vdim <= 0 || hd < rank) return -2;
+  if (n_tokens > HP_MANY) {
+    const dim3 grid((n_tokens + HP_BM - 1) / HP_BM, H, (vdim + HP_BN - 1) / HP_BN), block(256);
+#define CALL(T)                                                                                       \
+  launch_pdl(latent_expand_tiled_kernel<T>, grid, block, 0, stream, (const T*)o, (const T*)w_uv, gate, \
+             n_partials, partial_stride, (T*)out, n_tokens, H, rank, vdim, hd)
+    YALM_BY_TYPE(dtype, CALL);
+#undef CALL
+    YALM_LAUNCH_CHECK();
+    return 0;
+  }
   const size_t smem = (size_t)LT_TOK * rank * sizeof(float);
   if (smem > 48 * 1024) return -2;
   const dim3 grid((n_tokens + LT_TOK - 1) / LT_TOK, H), block(256);

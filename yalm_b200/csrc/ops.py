@@ -726,8 +726,8 @@ def residual_add(x: torch.Tensor, y: torch.Tensor, partials: Optional[torch.Tens
 
 def exact_attention_usable(dtype: torch.dtype, hd: int, chunk: Optional[int] = None) -> bool:
     """The tensor-core prefill attention that keeps its softmax weights in 32 bits takes bfloat16 or
-    float16, head sizes 32, 64 and 128, and a sliding window or none (no chunked mask)."""
-    return dtype in HALF_TYPES and hd in (32, 64, 128) and not chunk
+    float16, head sizes 32, 64, 128 and 256, and a sliding window or none (no chunked mask)."""
+    return dtype in HALF_TYPES and hd in (32, 64, 128, 256) and not chunk
 
 
 def attention_exact_prefill(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
