@@ -388,7 +388,7 @@ RUDAZEN_SIZES = {
                      rec_heads=32, rec_dim=128, rec_vdim=128, ff=11008, pattern="paap", vocab=32000),
 }
 def nekotar_config(width, wkv_heads, wkv_dim, decay_rank, lat_heads, lat_dim, rot_dim, lat_vdim, kv_rank,
-                   att_heads, att_kv, att_dim, window, keep, ff, pattern, vocab):
+                   att_heads, att_kv, att_dim, window, keep, ff, pattern, vocab, streams=4, mult=1.0):
     """A Nekotar configuration with layers of the sizes a served model has (random weights):
     ``pattern`` is a string of "w" (a wkv layer), "l" (latent attention with its own latent), "s"
     (latent attention reading the last "l" layer's latent) and "a" (windowed attention that keeps
@@ -411,13 +411,13 @@ def nekotar_config(width, wkv_heads, wkv_dim, decay_rank, lat_heads, lat_dim, ro
             layers.append({"type": "attention", "mlp": mlp,
                            "mixer": {"heads": att_heads, "kv_heads": att_kv, "dim": att_dim, "vdim": att_dim,
                                      "scale": float(att_dim) ** -0.5, "mask": {"size": window, "keep_first": keep},
-                                     "rot": {"base": 1e6, "dims": att_dim}}})
-    return {"architecture": "Nekotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "residual_mult": 0.5, "streams": 4, "layers": layers}
+                                     "rot": {"base": 5e5, "dims": att_dim}}})
+    return {"architecture": "Nekotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "residual_mult": mult, "streams": streams, "layers": layers}
 
 
 def nekotar_twin(width, wkv_heads, wkv_dim, decay_rank, lat_heads, lat_dim, rot_dim, lat_vdim, kv_rank,
-                 att_heads, att_kv, att_dim, window, keep, ff, pattern, vocab):
+                 att_heads, att_kv, att_dim, window, keep, ff, pattern, vocab, streams=4, mult=1.0):
     """The closest model the library had before: the Llama / Mistral decoder with the same width,
     layers and feed-forward, the windowed layers' heads and a sliding window of the same size."""
     return {"architectures": ["MistralForCausalLM"], "hidden_size": width, "intermediate_size": ff,
@@ -428,12 +428,12 @@ def nekotar_twin(width, wkv_heads, wkv_dim, decay_rank, lat_heads, lat_dim, rot_
 
 
 NEKOTAR_SIZES = {
-    "w2048-wwla": dict(width=2048, wkv_heads=32, wkv_dim=64, decay_rank=64, lat_heads=16, lat_dim=64, rot_dim=32,
-                       lat_vdim=64, kv_rank=96, att_heads=16, att_kv=4, att_dim=128, window=1024, keep=64,
-                       ff=5632, pattern="wwlawwsa", vocab=32000),
+    "w2048-wlas": dict(width=2048, wkv_heads=32, wkv_dim=64, decay_rank=64, lat_heads=16, lat_dim=64, rot_dim=64,
+                       lat_vdim=64, kv_rank=64, att_heads=16, att_kv=4, att_dim=128, window=1024, keep=64,
+                       ff=5632, pattern="wlwaswwa", vocab=32000),
     "w4096-wla": dict(width=4096, wkv_heads=64, wkv_dim=64, decay_rank=128, lat_heads=32, lat_dim=128, rot_dim=64,
                       lat_vdim=128, kv_rank=192, att_heads=32, att_kv=8, att_dim=128, window=2048, keep=128,
-                      ff=11008, pattern="wlaw", vocab=32000),
+                      ff=11008, pattern="wlaw", vocab=32000, mult=0.7),
 }
 DESIGNS = {"golulix": (DESIGN_SIZES, golulix_config, dense_twin),
            "rudazen": (RUDAZEN_SIZES, rudazen_config, rudazen_twin),

@@ -51,7 +51,7 @@ def _lm(cfg, w, dtype, **kw):
 
 # ------------------------------------------------------------------ kernels alone
 @pytest.mark.parametrize("copies", [1, 2, 3, 4, 8])
-@pytest.mark.parametrize("dim, rows", [(64, 5), (100, 3), (1000, 70), (4100, 2)])
+@pytest.mark.parametrize("dim, rows", [(64, 5), (100, 3), (1000, 70), (4100, 2), (30, 4), (2048, 300)])
 def test_residual_copies_write_and_read(ops, copies, dim, rows):
     g = torch.Generator().manual_seed(dim + copies)
     X = torch.randn(copies, rows, dim, generator=g)
