@@ -14,6 +14,7 @@ from .golulix import GolulixConfig
 from .llama import ConfigError, LlamaConfig
 from .nekotar import NekotarConfig
 from .rudazen import RudazenConfig
+from .samulorn import SamulornConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
 
@@ -54,3 +55,4 @@ register_architecture("MistralForCausalLM", LlamaConfig)
 register_architecture("Golulix", GolulixConfig)
 register_architecture("Rudazen", RudazenConfig)
 register_architecture("Nekotar", NekotarConfig)
+register_architecture("Samulorn", SamulornConfig)

@@ -220,8 +220,8 @@ int yalm_attention_exact_prefill(const void* q, const void* kv_step, const void*
 // sin are multiplied by `mult`.  Values: the v rows, or without them the keys as projected.
 int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long long partial_stride,
                             const float* bias, const float* q_norm, const float* k_norm, int n_q, int n_k, float eps,
-                            const float* freq, int dims, int neighbours, float mult,
-                            const int* token_seq, const int* q_start, const int* seq_slot,
+                            const float* freq, int dims, int neighbours, float mult, float head_eps,
+                            int head_size, const int* token_seq, const int* q_start, const int* seq_slot,
                             const int* slot_pos, void* q_out, void* kv_step, void* k_cache,
                             void* v_cache, int dtype, int n_tokens, int H, int G, int hd, int has_v,
                             int capacity, int write_cache, const int* page_table, int pages_per_slot,
@@ -282,8 +282,9 @@ int yalm_residual_add(float* x, const float* y, const float* partials, int n_par
 
 // ---- routed.cu: a routed feed-forward ----------------------------------------------------
 int yalm_route_topk(const float* z, int n_partials, long long partial_stride, int n_tokens, int E,
-                    int n_groups, int keep, int top, int renormalise, int* choice, float* weight,
-                    int* counts, cudaStream_t stream);
+                    int n_groups, int keep, int top, int renormalise, int sigmoid, int group_top2,
+                    float norm_eps, float weight_scale, const float* correction, int* choice,
+                    float* weight, int* counts, cudaStream_t stream);
 int yalm_route_plan(int* counts, const int* choice, int n_pairs, int top, int E, int tile_rows,
                     int* first_row, int* pair_row, int* row_token, int* tile_expert, int* tile_row0,
                     int* n_tiles, cudaStream_t stream);
@@ -345,6 +346,39 @@ int yalm_latent_expand(const void* o, const void* w_uv, const float* gate, int n
 // out [n] = act(sum of n_partials slices of z [n]): act 1 = gelu (tanh form), 2 = tanh
 int yalm_activation_rows(const float* z, int n_partials, long long partial_stride, void* out,
                          int out_dtype, long long n, int act, cudaStream_t stream);
+
+
+// ---- norm_step.cu: sublayer outputs that are normed before they join the residual stream ------------
+int yalm_norm_step(float* x, const float* a, int na, long long sa, float fa, const float* b, int nb,
+                   long long sb, float fb, int post_kind, const float* post_w, const float* post_b,
+                   float post_alpha, float post_eps, int pre_kind, const float* pre_w, const float* pre_b,
+                   float pre_alpha, float pre_eps, void* h, int h_dtype, const int* rows, int n_rows, int dim,
+                   cudaStream_t stream);
+int yalm_short_conv(const float* src, int n_partials, long long partial_stride, int src_row, int src_col0,
+                    const float* in_bias, const float* w, const float* out_bias, int taps, int channels,
+                    int silu, float* state, const int* token_seq, const int* q_start, const int* seq_slot,
+                    float* out32, int out_row, int out_col0, void* out16, int out16_dtype, int block16,
+                    int n_tokens, int n_seqs, int update_state, cudaStream_t stream);
+int yalm_gated_rows(const float* z, int n_partials, long long partial_stride, const int* tokens,
+                    const void* table, int table_dtype, int table_row, int first, void* out, int out_dtype,
+                    int n_tokens, int dim, cudaStream_t stream);
+
+// ---- delta_rule.cu: the gated delta rule with a decay per key channel ------------------------------
+int yalm_delta_row(int H, int G, int dk, int dv);
+int yalm_delta_prep(float* act, const float* proj, int n_partials, long long partial_stride, int proj_row,
+                    int col_b, int col_low, int n_low, void* low, int low_dtype, int n_tokens, int H, int G,
+                    int dk, int dv, cudaStream_t stream);
+int yalm_delta_scan(float* act, const float* z, int n_partials, long long partial_stride,
+                    const float* dt_bias, const float* a_log, float* gate, const int* q_start,
+                    const int* seq_slot, float* state, float* out, int n_tokens, int n_seqs, int H, int G,
+                    int dk, int dv, cudaStream_t stream);
+
+// ---- rglru.cu: a real-gated linear recurrent unit per channel ---------------------------------------
+int yalm_rglru(const float* gates, const float* ra_bias, const float* ri_bias, const float* lam,
+               const float* u, const float* yx, int n_partials, long long partial_stride, int yx_row,
+               const float* y_bias, float* coef, const int* q_start, const int* seq_slot, float* state,
+               void* out, int out_dtype, int n_tokens, int n_seqs, int width, int bw, float c_decay,
+               cudaStream_t stream);
 
 #ifdef __cplusplus
 }

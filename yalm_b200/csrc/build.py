@@ -26,7 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["elementwise.cu", "attention.cu", "attention_mma.cu", "attention_mma_prefill.cu",
            "attention_mma_fused.cu", "attention_mma_two_warps.cu", "attention_tc.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "sampling.cu",
            "small_ops.cu", "routed.cu", "sum_norm.cu", "qk_store.cu", "recurrence.cu", "attention_exact.cu",
-           "hyper.cu", "latent.cu"]
+           "hyper.cu", "latent.cu", "norm_step.cu", "delta_rule.cu", "rglru.cu"]
 HEADERS = ["api.h", "common.cuh", "attention_mma.cuh", "no_alloc.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]

@@ -84,7 +84,7 @@ _SIGNATURES = {
     "yalm_softcap": [_vp, _ll, _f, _vp],
     "yalm_element_gate": [_vp, _i, _vp, _i, _ll, _ll, _vp],
     "yalm_residual_add": [_vp, _vp, _vp, _i, _ll, _ll, _vp],
-    "yalm_route_topk": [_vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "yalm_route_topk": [_vp, _i, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp],
     "yalm_route_plan": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "yalm_gather_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "yalm_gemm_grouped": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -99,7 +99,7 @@ _SIGNATURES = {
                               _i, _i, _f, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_exact_prefill": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                                      _f, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _i, _i, _i, _vp],
-    "yalm_qk_norm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _vp, _i, _i, _f, _vp, _vp, _vp, _vp,
+    "yalm_qk_norm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _vp, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp,
                                 _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_pool_blocks": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i,
                          _i, _vp, _i, _i, _vp, _vp],
@@ -120,6 +120,16 @@ _SIGNATURES = {
     "yalm_latent_absorb_q": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "yalm_latent_expand": [_vp, _vp, _vp, _i, _ll, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "yalm_activation_rows": [_vp, _i, _ll, _vp, _i, _ll, _i, _vp],
+    "yalm_norm_step": [_vp, _vp, _i, _ll, _f, _vp, _i, _ll, _f, _i, _vp, _vp, _f, _f, _i, _vp, _vp, _f, _f, _vp,
+                       _i, _vp, _i, _i, _vp],
+    "yalm_short_conv": [_vp, _i, _ll, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp,
+                        _i, _i, _i, _i, _i, _vp],
+    "yalm_gated_rows": [_vp, _i, _ll, _vp, _vp, _i, _i, _i, _vp, _i, _i, _i, _vp],
+    "yalm_delta_row": [_i, _i, _i, _i],
+    "yalm_delta_prep": [_vp, _vp, _i, _ll, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "yalm_delta_scan": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "yalm_rglru": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                   _f, _vp],
 }
 
 _lib = None
@@ -764,12 +774,15 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_partials: int, q_norm: Optional[torc
                        q_out: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
                        v_cache: torch.Tensor, slot_pos: torch.Tensor, H: int, G: int, hd: int,
                        has_v: bool, capacity: int, write_cache: bool = True, pages=None,
-                       bias: Optional[torch.Tensor] = None) -> None:
+                       bias: Optional[torch.Tensor] = None, head_norm: Optional[tuple] = None) -> None:
     """qkv float32 [(s,) N, (H + G (+ G)) hd] -> q_out [N, H hd], kv_step [N, 2, G, hd] and the cache
     rows: q and k normed over their whole rows (n_q, n_k true features), the first ``dims``
     features of each head rotated (pairs (i, i + dims/2), or (2i, 2i+1) with ``neighbours``), cos
-    and sin times ``mult``; values are the v rows or, without them, the keys as projected."""
+    and sin times ``mult``; values are the v rows or, without them, the keys as projected.
+    ``head_norm`` = (eps, size): after the rotation every head of q and k is divided by its own root
+    mean square over ``size`` features (no weight; excludes the whole-row norms)."""
     n = q_out.shape[0]
+    head_eps, head_size = (float(head_norm[0]), int(head_norm[1])) if head_norm is not None else (-1.0, hd)
     row = (H + (2 if has_v else 1) * G) * hd
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[-1] == row
@@ -786,8 +799,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_partials: int, q_norm: Optional[torc
           "qk_norm_rope_store: bias float32 [row]")
     _check(lib().yalm_qk_norm_rope_store(
         _p(qkv), n_partials, n * row, _p(bias), _p(q_norm), _p(k_norm), int(n_q), int(n_k), float(eps), _p(freq),
-        int(dims), 1 if neighbours else 0, float(mult), _p(batch.token_seq), _p(batch.q_start),
-        _p(batch.seq_slot), _p(slot_pos), _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache),
+        int(dims), 1 if neighbours else 0, float(mult), head_eps, head_size, _p(batch.token_seq),
+        _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache),
         dtype_code(q_out.dtype), n, H, G, hd, 1 if has_v else 0, capacity, 1 if write_cache else 0, pt,
         pps, npg, _stream()), "qk_norm_rope_store")
 
@@ -1012,23 +1025,185 @@ def activation_rows(z: torch.Tensor, n_partials: int, out: torch.Tensor, act: in
                                       _stream()), "activation_rows")
 
 
+# ---- sublayer outputs normed before they join the residual stream -------------------------------------
+NORM_ABSENT, NORM_TANH, NORM_RMS, NORM_NONE = 0, 1, 2, 3
+
+
+def norm_step(x: torch.Tensor, sets=(), post: Optional[tuple] = None, pre: Optional[tuple] = None,
+              h: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+              n_rows: Optional[int] = None) -> None:
+    """One pass over the rows of x float32 [N, dim]: x <- x + post(y), then h = pre(x).  y is the sum
+    over ``sets`` (up to two (slices float32 [S, N, dim], S, factor)) of factor * sum of slices.  ``post``
+    and ``pre`` are (kind, weight, bias, alpha, eps) with kind NORM_TANH (tanh(alpha v) w + b),
+    NORM_RMS (v / sqrt(mean v^2 + eps) w) or NORM_NONE, or None for a step without that half.  With
+    ``rows`` (int32 row numbers; no post half) only those rows are read: h [n_rows, dim]."""
+    n, dim = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "norm_step: x float32 [N, dim]")
+    _need(len(sets) <= 2 and (post is None) == (len(sets) == 0), "norm_step: a post step has one or two sets")
+    args = []
+    for buf, S, factor in sets:
+        _need(buf.dtype == torch.float32 and buf.is_contiguous() and buf.numel() >= S * n * dim,
+              "norm_step: a set is float32 [S, N, dim]")
+        args += [_p(buf), int(S), n * dim, float(factor)]
+    while len(args) < 8:
+        args += [None, 0, 0, 0.0]
+    forms = []
+    for f in (post, pre):
+        if f is None:
+            forms += [NORM_ABSENT, None, None, 0.0, 0.0]
+            continue
+        kind, w, b, alpha, eps = f
+        _need(kind == NORM_NONE or (w is not None and w.dtype == torch.float32 and w.numel() == dim),
+              "norm_step: weight float32 [dim]")
+        _need(kind != NORM_TANH or (b is not None and b.dtype == torch.float32 and b.numel() == dim),
+              "norm_step: bias float32 [dim]")
+        forms += [int(kind), _p(w), _p(b), float(alpha), float(eps)]
+    count = n if rows is None else int(n_rows)
+    _need(pre is None or (h is not None and h.is_contiguous() and h.numel() >= count * dim), "norm_step: h")
+    _need(rows is None or (rows.dtype == torch.int32 and post is None), "norm_step: rows int32, no post half")
+    _check(lib().yalm_norm_step(_p(x), *args, *forms, _p(h), dtype_code(h.dtype) if h is not None else F32,
+                                _p(rows), count, dim, _stream()), "norm_step")
+
+
+def short_conv(src: torch.Tensor, n_partials: int, col0: int, channels: int, weight: torch.Tensor,
+               state: torch.Tensor, batch, out32: Optional[torch.Tensor] = None, out_col0: int = 0,
+               out16: Optional[torch.Tensor] = None, block16: Optional[int] = None,
+               in_bias: Optional[torch.Tensor] = None, out_bias: Optional[torch.Tensor] = None,
+               silu: bool = False) -> None:
+    """A causal convolution over time on ``channels`` columns (from ``col0``) of src, float32 slices
+    [(s,) N, row]: y_t = sum_j weight[c, j] u_(t - taps + 1 + j) (+ out_bias, then SiLU), u = the summed
+    slices (+ in_bias); the inputs before a step's first token come from ``state`` float32
+    [slots, taps - 1, channels], which leaves with the step's last ones.  out32: float32 [N, row'] at
+    column out_col0; out16: [channels / block16, N, block16] in its own type (block16 None: [N, channels])."""
+    n = batch.n_tokens
+    row = src.shape[-1]
+    taps = weight.shape[1]
+    _need(src.dtype == torch.float32 and src.is_contiguous() and src.shape[-2] == n and col0 + channels <= row,
+          "short_conv: float32 slices [(s,) N, row]")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == channels
+          and state.dtype == torch.float32 and state.is_contiguous()
+          and tuple(state.shape[1:]) == (taps - 1, channels), "short_conv: weight [channels, taps], state")
+    for b in (in_bias, out_bias):
+        _need(b is None or (b.dtype == torch.float32 and b.numel() == channels and b.is_contiguous()),
+              "short_conv: bias float32 [channels]")
+    _need(out32 is None or (out32.dtype == torch.float32 and out32.is_contiguous() and out32.shape[0] == n
+                            and out_col0 + channels <= out32.shape[1]), "short_conv: out32 float32 [N, row']")
+    _need(out16 is None or (out16.is_contiguous() and out16.numel() == n * channels), "short_conv: out16")
+    _need(out32 is not None or out16 is not None, "short_conv: no output")
+    update = not batch.is_decode
+    _check(lib().yalm_short_conv(_p(src), int(n_partials), n * row, row, int(col0), _p(in_bias), _p(weight),
+                                 _p(out_bias), taps, channels, 1 if silu else 0, _p(state), _p(batch.token_seq),
+                                 _p(batch.q_start), _p(batch.seq_slot), _p(out32),
+                                 out32.shape[1] if out32 is not None else 0, int(out_col0), _p(out16),
+                                 dtype_code(out16.dtype) if out16 is not None else F32,
+                                 int(block16 or channels), n, batch.n_seqs, 1 if update else 0, _stream()),
+           "short_conv", kernels=2 if update else 1)
+
+
+def gated_rows(z: torch.Tensor, n_partials: int, tokens: torch.Tensor, table: torch.Tensor, first: int,
+               out: torch.Tensor) -> None:
+    """out [N, dim] = gelu(sum of the slices of z float32 [(s,) N, dim]) * table[token, first : first + dim]
+    (gelu in its tanh form)."""
+    n, dim = out.shape
+    _need(z.dtype == torch.float32 and z.is_contiguous() and z.shape[-1] == dim and z.shape[-2] == n
+          and table.is_contiguous() and table.dim() == 2 and out.is_contiguous() and tokens.dtype == torch.int32,
+          "gated_rows: shapes")
+    _check(lib().yalm_gated_rows(_p(z), int(n_partials), n * dim, _p(tokens), _p(table), dtype_code(table.dtype),
+                                 table.shape[1], int(first), _p(out), dtype_code(out.dtype), n, dim, _stream()),
+           "gated_rows")
+
+
+# ---- the gated delta rule ----------------------------------------------------------------------------
+def delta_row(H: int, G: int, dk: int, dv: int) -> int:
+    """Floats in a token's activated row [q | k | v | beta (padded to 4) | decay]."""
+    return 2 * G * dk + H * dv + ((H + 3) & ~3) + H * dk
+
+
+def delta_prep(act: torch.Tensor, proj: torch.Tensor, n_partials: int, col_b: int, col_low: int, n_low: int,
+               low: torch.Tensor, H: int, G: int, dk: int, dv: int) -> None:
+    """act float32 [N, delta_row] holds q | k | v (after convolution and SiLU) in its first columns: q and
+    k become unit vectors per head (q also times dk^-1/2), beta = sigmoid of the H columns of ``proj``
+    (float32 slices [(s,) N, row]) from col_b, and the n_low columns from col_low go to ``low`` [N, n_low]
+    in low's type."""
+    n = act.shape[0]
+    _need(act.dtype == torch.float32 and act.is_contiguous() and act.shape[1] == delta_row(H, G, dk, dv)
+          and proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[-2] == n
+          and low.is_contiguous() and tuple(low.shape) == (n, n_low), "delta_prep: shapes")
+    row = proj.shape[-1]
+    _check(lib().yalm_delta_prep(_p(act), _p(proj), int(n_partials), n * row, row, int(col_b), int(col_low),
+                                 int(n_low), _p(low), dtype_code(low.dtype), n, H, G, dk, dv, _stream()),
+           "delta_prep")
+
+
+def delta_scan(act: torch.Tensor, z: torch.Tensor, n_partials: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+               gate: torch.Tensor, batch, state: torch.Tensor, out: torch.Tensor, H: int, G: int, dk: int,
+               dv: int) -> None:
+    """The decay exp(-exp(a_log[h]) softplus(z + dt_bias)) (z: float32 slices [(s,) N, H dk + H dv], decay
+    logits then gate logits; ``gate`` float32 [N, H dv] receives the gate's sigmoid), then per head
+    S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over the step's tokens.  ``state`` float32
+    [slots, H, dk, dv]; out float32 [N, H dv]."""
+    n = act.shape[0]
+    _need(act.dtype == torch.float32 and act.is_contiguous() and act.shape[1] == delta_row(H, G, dk, dv)
+          and z.dtype == torch.float32 and z.is_contiguous() and z.shape[-1] == H * dk + H * dv and z.shape[-2] == n
+          and dt_bias.dtype == a_log.dtype == torch.float32 and dt_bias.numel() == H * dk and a_log.numel() == H
+          and gate.dtype == torch.float32 and gate.numel() >= n * H * dv
+          and state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv)
+          and out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (n, H * dv),
+          "delta_scan: shapes")
+    _check(lib().yalm_delta_scan(_p(act), _p(z), int(n_partials), n * (H * dk + H * dv), _p(dt_bias), _p(a_log),
+                                 _p(gate), _p(batch.q_start), _p(batch.seq_slot), _p(state), _p(out), n,
+                                 batch.n_seqs, H, G, dk, dv, _stream()), "delta_scan", kernels=2)
+
+
+# ---- a real-gated linear recurrent unit ----------------------------------------------------------------
+def rglru(gates: torch.Tensor, ra_bias: torch.Tensor, ri_bias: torch.Tensor, lam: torch.Tensor, u: torch.Tensor,
+          yx: torch.Tensor, n_partials: int, y_bias: Optional[torch.Tensor], coef: torch.Tensor, batch,
+          state: torch.Tensor, out: torch.Tensor, width: int, bw: int, c_decay: float) -> None:
+    """a = exp(-c r softplus(lam)), S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t, out_t = S_t gelu(y_t + bias)
+    per channel over the step's tokens.  gates float32 [width / bw, N, 2 bw] (r logits, then i logits, of
+    every block of channels); u float32 [N, width]; yx float32 slices [(s,) N, row] with the y logits in
+    the first ``width`` columns; ``state`` float32 [slots, width]; out [N, width]."""
+    n = u.shape[0]
+    _need(gates.dtype == torch.float32 and gates.is_contiguous() and gates.numel() == 2 * n * width
+          and u.dtype == torch.float32 and u.is_contiguous() and u.shape[1] == width
+          and yx.dtype == torch.float32 and yx.is_contiguous() and yx.shape[-2] == n and yx.shape[-1] >= width
+          and coef.dtype == torch.float32 and coef.numel() >= 3 * n * width
+          and state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width
+          and out.is_contiguous() and tuple(out.shape) == (n, width), "rglru: shapes")
+    for v in (ra_bias, ri_bias, lam):
+        _need(v.dtype == torch.float32 and v.numel() == width and v.is_contiguous(), "rglru: float32 [width]")
+    row = yx.shape[-1]
+    _check(lib().yalm_rglru(_p(gates), _p(ra_bias), _p(ri_bias), _p(lam), _p(u), _p(yx), int(n_partials), n * row,
+                            row, _p(y_bias), _p(coef), _p(batch.q_start), _p(batch.seq_slot), _p(state), _p(out),
+                            dtype_code(out.dtype), n, batch.n_seqs, width, bw, float(c_decay), _stream()),
+           "rglru", kernels=2)
+
+
 # ---- a routed feed-forward --------------------------------------------------------------
 ROUTED_TILE = 64          # rows per tile of the grouped FMA product
 
 
 def route_topk(z: torch.Tensor, n_partials: int, n_tokens: int, E: int, n_groups: int, keep: int,
                top: int, renormalise: bool, choice: torch.Tensor, weight: torch.Tensor,
-               counts: torch.Tensor) -> None:
+               counts: torch.Tensor, sigmoid: bool = False, correction: Optional[torch.Tensor] = None,
+               group_top2: bool = False, norm_eps: float = 0.0, weight_scale: float = 1.0) -> None:
     """Router logits z (float32 slices [n_partials, n_tokens, E]) -> the ``top`` experts of each
-    token among the ``keep`` best of ``n_groups`` groups and their softmax scores."""
+    token among the ``keep`` best of ``n_groups`` groups and their scores.  Scores are the softmax
+    over all experts, or with ``sigmoid`` each logit's own sigmoid; ``correction`` float32 [E] is added
+    to the scores for the choice of groups and experts only; a group's score is its best choice
+    score, or with ``group_top2`` the sum of its two best; the weights are the chosen scores, with
+    ``renormalise`` divided by (their sum + ``norm_eps``), times ``weight_scale``."""
     _need(z.dtype == torch.float32 and z.is_contiguous() and z.numel() >= n_partials * n_tokens * E,
           "route_topk: logits")
     _need(choice.dtype == torch.int32 and weight.dtype == torch.float32 and counts.dtype == torch.int32
           and choice.numel() >= n_tokens * top and weight.numel() >= n_tokens * top
           and counts.numel() >= E, "route_topk: outputs")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.numel() == E
+                                 and correction.is_contiguous()), "route_topk: correction float32 [E]")
     _check(lib().yalm_route_topk(_p(z), n_partials, n_tokens * E, n_tokens, E, n_groups, keep, top,
-                                 1 if renormalise else 0, _p(choice), _p(weight), _p(counts), _stream()),
-           "route_topk")
+                                 1 if renormalise else 0, 1 if sigmoid else 0, 1 if group_top2 else 0,
+                                 float(norm_eps), float(weight_scale), _p(correction), _p(choice), _p(weight),
+                                 _p(counts), _stream()), "route_topk")
 
 
 def routed_max_tiles(n_pairs: int, E: int, tile_rows: int = ROUTED_TILE) -> int:

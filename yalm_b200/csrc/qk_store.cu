@@ -6,7 +6,8 @@
 //    (i, i + dims/2) or neighbours (2i, 2i+1) -- by pos * freq[i] with cos and sin times `mult`,
 //    and writes q, this step's keys and values and the cache rows in the storage type.  The
 //    values are the v rows of the product, or, when it has none, the keys as projected
-//    (before norm and rotation);
+//    (before norm and rotation).  With head_eps >= 0 every head of q and k is, AFTER its rotation,
+//    divided by its own root mean square over head_size features (a norm without a weight);
 //  * pool_blocks: the mean key and the mean value of every block of `pool` positions that
 //    this step completes, from the rows as the cache holds them, into a second cache that has
 //    one row per block.
@@ -24,7 +25,7 @@ template <typename T>
 __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ qkv, int n_partials, long long partial_stride,
     const float* __restrict__ bias, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float n_q, float n_k, float eps,
-    const float* __restrict__ freq, int dims, int neighbours, float mult,
+    const float* __restrict__ freq, int dims, int neighbours, float mult, float head_eps, float head_size,
     const int* __restrict__ token_seq, const int* __restrict__ q_start,
     const int* __restrict__ seq_slot, const int* __restrict__ slot_pos, T* __restrict__ q_out,
     T* __restrict__ kv_step, T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G, int hd,
@@ -61,6 +62,34 @@ __global__ void qk_norm_rope_store_kernel(
   if (k_norm != nullptr) rk = 1.0f / sqrtf(block_sum(ssk, scratch) / n_k + eps);
   __syncthreads();
   const int half = dims >> 1;
+  // a norm per head after the rotation: the rotated row replaces the summed one first
+  float* head_r = reinterpret_cast<float*>(cs + half);              // [H + G]
+  if (head_eps >= 0.f) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int head = warp; head < H + G; head += n_warps) {
+      float* v = row_s + (size_t)head * hd;
+      float ss = 0.f;
+      if (neighbours) {
+        for (int p = lane; p < half; p += 32) {
+          const float a = v[2 * p], b2 = v[2 * p + 1];
+          const float lo = rotate_lo(a, b2, cs[p].x, cs[p].y), hi = rotate_hi(a, b2, cs[p].x, cs[p].y);
+          v[2 * p] = lo; v[2 * p + 1] = hi;
+          ss += lo * lo + hi * hi;
+        }
+      } else {
+        for (int p = lane; p < half; p += 32) {
+          const float a = v[p], b2 = v[p + half];
+          const float lo = rotate_lo(a, b2, cs[p].x, cs[p].y), hi = rotate_hi(a, b2, cs[p].x, cs[p].y);
+          v[p] = lo; v[p + half] = hi;
+          ss += lo * lo + hi * hi;
+        }
+      }
+      for (int e = dims + lane; e < hd; e += 32) ss += v[e] * v[e];
+      ss = warp_sum(ss);
+      if (lane == 0) head_r[head] = 1.0f / sqrtf(ss / head_size + head_eps);
+    }
+    __syncthreads();
+  }
   // this block's part of the outputs
   const int per_part = (nq + nk + gridDim.y - 1) / gridDim.y;
   const int i_lo = blockIdx.y * per_part, i_hi = min(nq + nk, i_lo + per_part);
@@ -74,7 +103,9 @@ __global__ void qk_norm_rope_store_kernel(
     const float* w = is_q ? q_norm : k_norm;
     const float r = is_q ? rq : rk;
     float me = row_s[i] * (w != nullptr ? r * w[j] : 1.f);
-    if (e < dims) {
+    if (head_eps >= 0.f) {
+      me *= head_r[is_q ? head : H + head];
+    } else if (e < dims) {
       int pi, pair;                                       // partner's feature, pair number
       bool first;
       if (neighbours) { pi = e ^ 1; pair = e >> 1; first = !(e & 1); }
@@ -158,7 +189,7 @@ using namespace yalm;
 extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long long partial_stride,
                                        const float* bias, const float* q_norm, const float* k_norm, int n_q, int n_k,
                                        float eps, const float* freq, int dims, int neighbours,
-                                       float mult, const int* token_seq, const int* q_start,
+                                       float mult, float head_eps, int head_size, const int* token_seq, const int* q_start,
                                        const int* seq_slot, const int* slot_pos, void* q_out,
                                        void* kv_step, void* k_cache, void* v_cache, int dtype,
                                        int n_tokens, int H, int G, int hd, int has_v, int capacity,
@@ -167,8 +198,9 @@ extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long lo
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || dims < 0 || dims > hd || (dims & 1) || H <= 0 || G <= 0 || n_q <= 0 || n_k <= 0) return -2;
   const int row = (H + (has_v ? 2 : 1) * G) * hd;
-  const size_t smem = (size_t)(((row + 1) & ~1) + dims) * sizeof(float);
+  const size_t smem = (size_t)(((row + 1) & ~1) + dims + H + G) * sizeof(float);
   if (smem > 200 * 1024) return -2;
+  if (head_eps >= 0.f && (head_size <= 0 || head_size > hd || q_norm != nullptr || k_norm != nullptr)) return -3;
   const int threads = row >= 2048 ? 512 : (row >= 512 ? 256 : 128);
   // a few tokens (a decode step): several blocks per token, each with a part of the outputs
   int parts = 1;
@@ -188,7 +220,7 @@ extern "C" int yalm_qk_norm_rope_store(const float* qkv, int n_partials, long lo
     }                                                                                                 \
     launch_pdl(qk_norm_rope_store_kernel<T>, dim3(n_tokens, parts), dim3(threads), smem, stream, qkv, \
                n_partials, partial_stride, bias, q_norm, k_norm, (float)n_q, (float)n_k, eps, freq, dims,   \
-               neighbours, mult, token_seq, q_start, seq_slot, slot_pos, (T*)q_out, (T*)kv_step,      \
+               neighbours, mult, head_eps, (float)head_size, token_seq, q_start, seq_slot, slot_pos, (T*)q_out, (T*)kv_step,      \
                (T*)k_cache, (T*)v_cache, H, G, hd, has_v, capacity, write_cache, page_table,          \
                pages_per_slot, n_pages);                                                              \
   } while (0)

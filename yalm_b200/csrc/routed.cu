@@ -27,9 +27,21 @@ namespace yalm {
 
 constexpr int RT_WARPS = 4;
 
+// What differs between designs is a parameter: `sigmoid` (scores = sigmoid(z) instead of the softmax
+// over all experts), `correction` (a stored offset per expert that is added to the scores for the
+// CHOICE of groups and experts only; the weights use the scores themselves), `group_top2` (a group's
+// score is the sum of its two best choice scores instead of its best one), `norm_eps` (added to the
+// sum the chosen scores are divided by) and `weight_scale` (a factor on the final weights).  Choice
+// scores may be negative, so "not eligible" and "taken" are minus infinity.
+struct RouteRule {
+  int sigmoid, group_top2, renormalise;
+  float norm_eps, weight_scale;
+  const float* correction;
+};
+
 __global__ void __launch_bounds__(RT_WARPS * 32)
 route_topk_kernel(const float* __restrict__ z, int n_partials, long long partial_stride,
-                  int n_tokens, int E, int n_groups, int keep, int top, int renormalise,
+                  int n_tokens, int E, int n_groups, int keep, int top, RouteRule rule,
                   int* __restrict__ choice, float* __restrict__ weight, int* __restrict__ counts) {
   pdl_launch_dependents();
   pdl_wait();
@@ -37,8 +49,9 @@ route_topk_kernel(const float* __restrict__ z, int n_partials, long long partial
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * RT_WARPS + warp;
   if (t >= n_tokens) return;
-  float* score = rt_smem + (size_t)warp * (2 * E + n_groups);     // softmax over all experts
-  float* cand = score + E;                                        // the same, taken ones removed
+  float* score = rt_smem + (size_t)warp * (3 * E + n_groups);     // the scores the weights are made of
+  float* pick = score + E;                                        // the scores the choice goes by
+  float* cand = pick + E;                                         // pick of the eligible experts, taken ones removed
   float* gbest = cand + E;
   const int per = E / n_groups;
 
@@ -48,26 +61,37 @@ route_topk_kernel(const float* __restrict__ z, int n_partials, long long partial
     score[e] = v;
     m = fmaxf(m, v);
   }
-  m = warp_max(m);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float p = expf(score[e] - m);
-    score[e] = p;
-    sum += p;
+  if (rule.sigmoid) {
+    for (int e = lane; e < E; e += 32) score[e] = 1.0f / (1.0f + expf(-score[e]));
+  } else {
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(score[e] - m);
+      score[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
   }
-  sum = warp_sum(sum);
-  for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
+  for (int e = lane; e < E; e += 32) {
+    pick[e] = score[e] + (rule.correction != nullptr ? rule.correction[e] : 0.f);
+    cand[e] = -INFINITY;
+  }
   __syncwarp();
   for (int g = lane; g < n_groups; g += 32) {
-    float b = -1.f;
-    for (int i = 0; i < per; ++i) b = fmaxf(b, score[g * per + i]);
-    gbest[g] = b;
+    float b = -INFINITY, b2 = -INFINITY;                          // the group's best and second best
+    for (int i = 0; i < per; ++i) {
+      const float v = pick[g * per + i];
+      if (v > b) { b2 = b; b = v; }
+      else if (v > b2) b2 = v;
+    }
+    gbest[g] = (rule.group_top2 && per > 1) ? b + b2 : b;
   }
-  for (int e = lane; e < E; e += 32) cand[e] = -1.f;              // scores are >= 0
   __syncwarp();
   // the `keep` best groups, one at a time: (largest score, lowest index)
   for (int r = 0; r < keep; ++r) {
-    float bv = -2.f;
+    float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int g = lane; g < n_groups; g += 32)
       if (gbest[g] > bv) { bv = gbest[g]; bi = g; }
@@ -78,14 +102,14 @@ route_topk_kernel(const float* __restrict__ z, int n_partials, long long partial
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if (bi < n_groups) {
-      for (int i = lane; i < per; i += 32) cand[bi * per + i] = score[bi * per + i];
-      if (lane == 0) gbest[bi] = -3.f;
+      for (int i = lane; i < per; i += 32) cand[bi * per + i] = pick[bi * per + i];
+      if (lane == 0) gbest[bi] = -INFINITY;
     }
     __syncwarp();
   }
   float wsum = 0.f;
   for (int j = 0; j < top; ++j) {
-    float bv = -2.f;
+    float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32)
       if (cand[e] > bv) { bv = cand[e]; bi = e; }
@@ -96,17 +120,22 @@ route_topk_kernel(const float* __restrict__ z, int n_partials, long long partial
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if (bi >= E) bi = 0;                    // fewer eligible experts than `top`: refused on the host
-    wsum += bv;
+    const float sv = score[bi];
+    wsum += sv;
     if (lane == 0) {
       choice[(size_t)t * top + j] = bi;
-      weight[(size_t)t * top + j] = bv;
+      weight[(size_t)t * top + j] = sv;
       atomicAdd(&counts[bi], 1);
-      cand[bi] = -3.f;
+      cand[bi] = -INFINITY;
     }
     __syncwarp();
   }
-  if (renormalise && lane == 0)
-    for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] /= wsum;
+  if (lane == 0) {
+    if (rule.renormalise)
+      for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] /= (wsum + rule.norm_eps);
+    if (rule.weight_scale != 1.0f)
+      for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] *= rule.weight_scale;
+  }
 }
 
 // One block.  counts [E] comes in as the number of pairs per expert and leaves as zeros.
@@ -330,16 +359,18 @@ using namespace yalm;
 // z: router logits as n_partials float32 slices [n_tokens, E].  choice / weight [n_tokens, top];
 // counts [E] int32, zero before the call: pairs per expert afterwards.
 extern "C" int yalm_route_topk(const float* z, int n_partials, long long partial_stride, int n_tokens,
-                               int E, int n_groups, int keep, int top, int renormalise, int* choice,
-                               float* weight, int* counts, cudaStream_t stream) {
+                               int E, int n_groups, int keep, int top, int renormalise, int sigmoid,
+                               int group_top2, float norm_eps, float weight_scale, const float* correction,
+                               int* choice, float* weight, int* counts, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (E <= 0 || n_groups <= 0 || E % n_groups || keep <= 0 || keep > n_groups || top <= 0 ||
       top > keep * (E / n_groups))
     return -2;
-  const size_t smem = (size_t)RT_WARPS * (2 * E + n_groups) * sizeof(float);
+  const size_t smem = (size_t)RT_WARPS * (3 * E + n_groups) * sizeof(float);
   if (smem > 48 * 1024) return -2;
+  const RouteRule rule = {sigmoid, group_top2, renormalise, norm_eps, weight_scale, correction};
   launch_pdl(route_topk_kernel, dim3((n_tokens + RT_WARPS - 1) / RT_WARPS), dim3(RT_WARPS * 32), smem,
-             stream, z, n_partials, partial_stride, n_tokens, E, n_groups, keep, top, renormalise, choice,
+             stream, z, n_partials, partial_stride, n_tokens, E, n_groups, keep, top, rule, choice,
              weight, counts);
   YALM_LAUNCH_CHECK();
   return 0;

@@ -1,5 +1,5 @@
-from . import (attention, block, embedding, feedforward, latent, norm, parallel, position,  # noqa: F401 (register)
-               recurrence, wkv)
+from . import (attention, block, delta, embedding, feedforward, latent, norm, parallel, position,  # noqa: F401 (register)
+               recurrence, rglru, wkv)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS,
                    ResidualStream, Runtime, make_part, register_block, register_embedding,
                    register_feed_forward, register_head, register_mixer, register_norm,

@@ -37,6 +37,12 @@ Options beyond that, each a parameter (all off for the Llama / Mistral decoder):
 * ``keep_first`` = F (with a window W): a query also sees the positions below F, at their own
   positions (for rotation and distance), however far back they lie.  The cache then keeps every
   position instead of a ring of W rows;
+* ``conv`` = taps: a short causal convolution over time on every channel of q, k and v
+  (``q.conv``, ``k.conv``, ``v.conv`` [channels, taps], the last column the current token's), directly
+  after the projection and its bias, before norm and rotation; the last taps - 1 projected rows of
+  a sequence are a fixed-size cache need beside its keys and values;
+* ``head_norm`` = {"eps": e}: after the rotation every head of q and k is divided by its own root mean
+  square (a norm without a weight; needs the ``rope_partial`` encoding);
 * ``exact_softmax``: scores, softmax weights and the weighted sum of values in 32-bit arithmetic
   (the FMA attention kernels on the 16-bit cache) instead of the tensor-core kernels, whose
   weights are rounded to 16 bits.
@@ -105,6 +111,15 @@ class GQAAttention:
         self.exact = bool(params.get("exact_softmax", False))
         self.bias = bool(params.get("bias", False))
         self.keep_first: Optional[int] = params.get("keep_first") or None
+        self.conv: Optional[int] = int(params["conv"]) if params.get("conv") else None
+        self.head_norm = params.get("head_norm") or None
+        if (self.conv or self.head_norm) and params["position"].kind != "rope_partial":
+            raise ValueError("a convolution after the projection and a norm per head after the rotation "
+                             "need the rope_partial encoding")
+        if self.conv is not None and not 2 <= self.conv <= 8:
+            raise ValueError(f"a convolution of {self.conv} taps (2 to 8)")
+        if self.head_norm and params.get("qk_norm"):
+            raise ValueError("a norm per head and whole-projection norms exclude each other")
         if self.keep_first and not self.window:
             raise ValueError("kept first positions stay visible beside a sliding window: the mixer needs one")
         if self.keep_first and self.pool:
@@ -172,6 +187,11 @@ class GQAAttention:
             needs["k.b"] = TensorNeed((self.G * self.hd_k,), init="around_zero")
             if not self.values_from_keys:
                 needs["v.b"] = TensorNeed((self.G * self.hd_v,), init="around_zero")
+        if self.conv:
+            needs["q.conv"] = TensorNeed((self.H * self.hd_k, self.conv))
+            needs["k.conv"] = TensorNeed((self.G * self.hd_k, self.conv))
+            if not self.values_from_keys:
+                needs["v.conv"] = TensorNeed((self.G * self.hd_v, self.conv))
         return needs
 
     def _pad_vector(self, w: torch.Tensor, heads: int, size: int) -> torch.Tensor:
@@ -224,8 +244,16 @@ class GQAAttention:
             if not self.values_from_keys:
                 b.append(self._pad_vector(tensors["v.b"], self.G, self.hd_v))
             self._store_extras["bias"] = torch.cat(b).contiguous()
+        if self.conv:
+            c = [self._pad_heads(self.rt.vector(tensors["q.conv"]), self.H, self.hd_k),
+                 self._pad_heads(self.rt.vector(tensors["k.conv"]), self.G, self.hd_k)]
+            if not self.values_from_keys:
+                c.append(self._pad_heads(self.rt.vector(tensors["v.conv"]), self.G, self.hd_v))
+            self.conv_w = torch.cat(c, 0).contiguous()
+        if self.head_norm:
+            self._store_extras["head_norm"] = (float(self.head_norm["eps"]), self.hd_k)
 
-    def cache_need(self):
+    def _kv_need(self):
         if self.keep_first:
             # every position stays (the first ones are seen for ever); the mask alone bounds the keys
             return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=None)
@@ -234,6 +262,15 @@ class GQAAttention:
         # the ring keeps a completing block's rows; the pooled rows are never dropped
         return {"kv": CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=max(self.window, self.pool)),
                 "pool": CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=None, every=self.pool)}
+
+    def cache_need(self):
+        need = self._kv_need()
+        if not self.conv:
+            return need
+        rows = (self.H + (1 if self.values_from_keys else 2) * self.G) * self.hd
+        needs = dict(need) if isinstance(need, dict) else {"kv": need}
+        needs["conv"] = CacheNeed("state", state_shape=(self.conv - 1, rows), state_dtype=torch.float32)
+        return needs
 
     def decode_chunk(self, batch) -> int:
         """Keys per block of the decode kernel: 64 KiB of keys and values, so
@@ -328,10 +365,12 @@ class GQAAttention:
     def forward(self, h, batch, stream, view, shared: bool = False):
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
         n = batch.n_tokens
-        pool_view = None
+        pool_view = conv_view = None
         if isinstance(view, dict):
-            pool_view, view = view["pool"], view["kv"]
+            pool_view, conv_view, view = view.get("pool"), view.get("conv"), view["kv"]
         extras = self._store_extras
+        if self.conv and shared:
+            raise RuntimeError("a convolved projection cannot read another run entry's cache")
         q = rt.buffer("q_rot", (n, H * hd), rt.dtype)
         # many tokens: the q/k/v product rotates and stores in its own epilogue
         table = getattr(self.position, "step_table", None)
@@ -339,6 +378,14 @@ class GQAAttention:
                  and ops.gemm_2sm_rope_usable(h, self.w_qkv, hd))
         if not fused:
             qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
+        if self.conv:
+            # bias, then the convolution over time, in 32 bits; the store kernel goes on from its output
+            rows = self.w_qkv.shape[0]
+            conv = rt.buffer("qkv_conv", (1, n, rows), torch.float32)
+            ops.short_conv(qkv, S, 0, rows, self.conv_w, conv_view.state, batch, out32=conv[0],
+                           in_bias=extras.get("bias"))
+            qkv, S = conv, 1
+            extras = {k: v for k, v in extras.items() if k != "bias"}
         if self.head_gate or self.element_gate:
             gate, gate_S = matmul_partials(rt, h, self.w_g, "head_gate")
         mask = {"chunk": self.chunk, "scale": self.scale}

@@ -218,6 +218,10 @@ class ResidualStream:
         self.copies: Optional[torch.Tensor] = None
         self._copy_write = None                        # (slices, S, mix, out weights, factor)
         self._ones: Optional[torch.Tensor] = None
+        # A block that norms a sublayer's OUTPUT before the sum (x <- x + post(y)): the write is
+        # left here as (sets of slices, the norm's form) and performed by whatever reads x next, in
+        # the same kernel as that read (``read_norm``), or on its own (``settle``).
+        self.due = None
 
     # -- several residual copies --------------------------------------------------------------
     def spread(self, ones: torch.Tensor) -> None:
@@ -261,6 +265,46 @@ class ResidualStream:
             self._copy_write = None
         return self.copies.sum(0)
 
+    # -- sublayer outputs that are normed before the sum ----------------------------------------
+    def post_norm(self, form) -> None:
+        """x <- x + n(y), with n given by ``form`` = (kind, weight, bias, alpha, eps) as
+        ``ops.norm_step`` takes it and y what the sublayer left on the held stream: the slices of its
+        last product, or the scaled sum of a two-branch mixer's products.  Done by the next read."""
+        self.settle()
+        if self.branches:
+            if any(w is not None for _, _, w, _ in self.branches):
+                raise RuntimeError("branches with norms of their own need a norm that sums them (sum_rmsnorm)")
+            sets = [(buf, S, factor) for buf, S, _, factor in self.branches]
+            self.branches = []
+        elif self.n_pending:
+            sets = [(self.pending, self.n_pending, 1.0)]
+            self.pending, self.n_pending = None, 0
+        else:
+            raise RuntimeError("the sublayer left no output on the stream")
+        self.due, self.h = (sets, form), None
+
+    def settle(self) -> None:
+        """Performs the write that ``post_norm`` left."""
+        if self.due is not None:
+            sets, form = self.due
+            self.due = None
+            ops.norm_step(self.x, sets, post=form)
+
+    def read_norm(self, form, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                  n_rows: Optional[int] = None) -> torch.Tensor:
+        """out = n(x) for the norm ``form``, after the write that is due (both in one kernel); pending
+        slices of a product that was not held are added on the way.  With ``rows`` only those rows."""
+        sets, post = self.due if self.due is not None else ((), None)
+        self.due = None
+        if post is None and self.n_pending:
+            sets, post = [(self.pending, self.n_pending, 1.0)], (ops.NORM_NONE, None, None, 0.0, 0.0)
+            self.pending, self.n_pending = None, 0
+        if rows is not None and post is not None:
+            ops.norm_step(self.x, sets, post=post)
+            sets, post = (), None
+        ops.norm_step(self.x, sets, post=post, pre=form, h=out, rows=rows, n_rows=n_rows)
+        return out
+
     def as_input(self) -> torch.Tensor:
         """x itself as the input of a product: in the compute type (a copy that the last norm
         made, or one made here), or x where the compute type is 32-bit."""
@@ -287,6 +331,7 @@ class ResidualStream:
     def resolve(self) -> torch.Tensor:
         if self.branches:
             raise RuntimeError("normed branches are pending: only a norm that sums them can resolve the stream")
+        self.settle()
         self.h = None
         if self.n_pending:
             self.x += self.pending[:self.n_pending].sum(0)

@@ -132,3 +132,67 @@ class HyperPreNormBlock:
         finally:
             stream.hold = False
         return later
+
+
+@register_block("prepost_norm")
+class PrePostNormBlock:
+    """Every sublayer is normed before AND after: x <- x + post(f(pre(x))), for the mixer, then the
+    feed-forward (optional), then an optional third sublayer ``extra`` that reads x itself (no norm
+    before it) and is normed after.  The norms after a sublayer hand their form to the stream
+    (``ResidualStream.post_norm``), which performs the write together with the next read; the parts
+    are ``mixer_norm``, ``mixer``, ``mixer_post_norm``, ``feed_forward_norm``, ``feed_forward``,
+    ``feed_forward_post_norm``, ``extra``, ``extra_post_norm``."""
+
+    def __init__(self, layer_spec, rt):
+        self.spec = layer_spec
+        self.rt = rt
+        self.mixer_norm = make_part(NORMS, layer_spec.part("mixer_norm"), rt)
+        self.mixer = make_part(MIXERS, layer_spec.part("mixer"), rt)
+        self.mixer_post = make_part(NORMS, layer_spec.part("mixer_post_norm"), rt)
+        self.ffn = self.ffn_norm = self.ffn_post = self.extra = self.extra_post = None
+        if "feed_forward" in layer_spec.parts:
+            self.ffn_norm = make_part(NORMS, layer_spec.part("feed_forward_norm"), rt)
+            self.ffn = make_part(FEED_FORWARDS, layer_spec.part("feed_forward"), rt)
+            self.ffn_post = make_part(NORMS, layer_spec.part("feed_forward_post_norm"), rt)
+        if "extra" in layer_spec.parts:
+            self.extra = make_part(FEED_FORWARDS, layer_spec.part("extra"), rt)
+            self.extra_post = make_part(NORMS, layer_spec.part("extra_post_norm"), rt)
+        for n in (self.mixer_post, self.ffn_post, self.extra_post):
+            if n is not None and not hasattr(n, "form"):
+                raise TypeError("a prepost_norm block needs output norms that give their form (dynamic_tanh, rmsnorm)")
+
+    def parts(self):
+        s = self.spec
+        names = ["mixer_norm", "mixer", "mixer_post_norm"]
+        if self.ffn is not None:
+            names += ["feed_forward_norm", "feed_forward", "feed_forward_post_norm"]
+        if self.extra is not None:
+            names += ["extra", "extra_post_norm"]
+        built = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_post_norm": self.mixer_post,
+                 "feed_forward_norm": self.ffn_norm, "feed_forward": self.ffn,
+                 "feed_forward_post_norm": self.ffn_post, "extra": self.extra, "extra_post_norm": self.extra_post}
+        return [(built[n], s.part(n)) for n in names]
+
+    def mixers(self):
+        return {"mixer": self.mixer}
+
+    def forward(self, stream, batch, views, shared: bool = False):
+        from ..csrc import ops
+        stream.hold = True
+        try:
+            h = self.mixer_norm(stream)
+            later = self.mixer.forward(h, batch, stream, views["mixer"], shared=shared)
+            stream.post_norm(self.mixer_post.form())
+            if self.ffn is not None:
+                h = self.ffn_norm(stream)
+                self.ffn.forward(h, batch, stream)
+                stream.post_norm(self.ffn_post.form())
+            if self.extra is not None:
+                # the third sublayer reads the stream as it is, in the compute type
+                h = self.rt.buffer("stream_input", tuple(stream.x.shape), self.rt.dtype)
+                stream.read_norm((ops.NORM_NONE, None, None, 0.0, 0.0), h)
+                self.extra.forward(h, batch, stream)
+                stream.post_norm(self.extra_post.form())
+        finally:
+            stream.hold = False
+        return later

@@ -129,6 +129,11 @@ class RoutedExperts:
     largest expert score, only experts of the ``keep_groups`` best groups are eligible, each
     token uses the ``top`` eligible experts with the largest scores, weighted by those scores
     (divided by their sum with ``renormalise``); x += sum_j w_j expert_j(h) + shared(h).
+    Other routing rules are parameters: ``score`` "sigmoid" (each logit's own sigmoid instead of the
+    softmax), ``correction`` (a stored offset per expert, added to the scores for the choice only; the
+    weights use the scores themselves), ``group_score`` "top2" (a group's score is the sum of its two
+    best choice scores), ``norm_eps`` (added to the sum the weights are divided by) and
+    ``weight_scale`` (a factor on the weights).
 
     The step: router product -> ``route_topk`` -> ``route_plan`` (the (token, choice) pairs
     sorted by expert, on the device: nothing comes back to the host, so a decode step with
@@ -148,6 +153,15 @@ class RoutedExperts:
         self.limit = float(params.get("limit") or 0.0)
         self.slope = float(params.get("slope", 1.0))
         self.shift = float(params.get("shift", 0.0))
+        if params.get("score", "softmax") not in ("softmax", "sigmoid") \
+                or params.get("group_score", "max") not in ("max", "top2"):
+            raise ValueError("routed_experts: score is 'softmax' or 'sigmoid', group_score 'max' or 'top2'")
+        self.sigmoid = params.get("score", "softmax") == "sigmoid"
+        self.group_top2 = params.get("group_score", "max") == "top2"
+        self.has_correction = bool(params.get("correction", False))
+        self.norm_eps = float(params.get("norm_eps") or 0.0)
+        self.weight_scale = float(params.get("weight_scale", 1.0))
+        self.correction = None
         if self.E % self.groups or not 0 < self.keep <= self.groups:
             raise ValueError(f"{self.E} experts do not form {self.groups} equal groups "
                              f"of which {self.keep} are kept")
@@ -166,10 +180,14 @@ class RoutedExperts:
             needs[f"down.{j}"] = TensorNeed((self.D, self.F))
         if self.shared is not None:
             needs.update(self.shared.tensor_needs("shared."))
+        if self.has_correction:
+            needs["correction"] = TensorNeed((self.E,), init="around_zero")
         return needs
 
     def bind(self, tensors) -> None:
         self.w_router = self.rt.matrix(tensors["router"])
+        if self.has_correction:
+            self.correction = self.rt.vector(tensors["correction"])
         names = [f"{k}.{j}" for j in range(self.E) for k in ("gate", "up", "down")]
         wide = any(tensors[n].dtype == torch.float32 for n in names)
         get = lambda n: tensors[n].to(torch.float32) if wide else tensors[n]
@@ -204,7 +222,9 @@ class RoutedExperts:
         choice = rt.buffer("routed_choice", (pairs,), i32)
         weight = rt.buffer("routed_weight", (pairs,), torch.float32)
         counts = rt.zeros("routed_counts", E)
-        ops.route_topk(z, S, n, E, self.groups, self.keep, top, self.renormalise, choice, weight, counts)
+        ops.route_topk(z, S, n, E, self.groups, self.keep, top, self.renormalise, choice, weight, counts,
+                       sigmoid=self.sigmoid, correction=self.correction, group_top2=self.group_top2,
+                       norm_eps=self.norm_eps, weight_scale=self.weight_scale)
         # 16-bit operands that TMA can address: both grouped products on tcgen05, the activation
         # in the first one's epilogue; else the FMA kernel (the 32-bit path among others)
         tensor_cores = (rt.gemm != "simt" and h.dtype in ops.HALF_TYPES and self.w_down.dtype == h.dtype
@@ -233,6 +253,54 @@ class RoutedExperts:
             ops.gemm_grouped(rows, self.w_gate_up, gu, *plan)
             ops.glu_clamp(gu, act, 1, self.slope, self.limit, self.shift)
             ops.gemm_grouped(act, self.w_down, y, *plan)
+        if getattr(stream, "hold", False):
+            # the block norms the output before the sum: the weighted sum is formed apart from x
+            if self.shared is not None:
+                raise RuntimeError("a shared expert beside a held stream is not supported")
+            out = rt.buffer("routed_sum", (1, n, D), torch.float32)
+            out.zero_()
+            ops.routed_combine(out[0], y, pair_row, weight, top)
+            stream.pending, stream.n_pending = out, 1
+            return
         ops.routed_combine(stream.resolve(), y, pair_row, weight, top)
         if self.shared is not None:
             self.shared.forward(h, stream, "shared_expert")
+
+
+@register_feed_forward("token_side_input")
+class TokenSideInput:
+    """A sublayer that feeds the token itself in again: with e the ``dim`` columns from ``first`` of a
+    second embedding table's row for the token, y = Wp (gelu(Wg x) * e), gelu in its tanh form.  x is
+    what the block hands it (the residual stream itself in a ``prepost_norm`` block's third place);
+    the block's output norm takes y from the stream."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.D = int(params["hidden_size"])
+        self.dim = int(params["dim"])
+        self.vocab = int(params["vocab_size"])
+        self.table_width = int(params["table_width"])
+        self.first = int(params["first"])
+        if not 0 <= self.first <= self.table_width - self.dim:
+            raise ValueError(f"token_side_input: columns {self.first} .. {self.first + self.dim} of a table "
+                             f"{self.table_width} wide")
+        self.table = self.w_gate = self.w_proj = None
+
+    def tensor_needs(self):
+        return {"table": TensorNeed((self.vocab, self.table_width)), "gate": TensorNeed((self.dim, self.D)),
+                "proj": TensorNeed((self.D, self.dim))}
+
+    def bind(self, tensors) -> None:
+        self.table = self.rt.matrix(tensors["table"], share=True)
+        self.w_gate = self.rt.matrix(tensors["gate"])
+        self.w_proj = self.rt.matrix(tensors["proj"])
+
+    def flops(self, q_lens, past) -> float:
+        return 2.0 * sum(q_lens) * 2 * self.dim * self.D
+
+    def forward(self, h, batch, stream) -> None:
+        rt = self.rt
+        z, S = matmul_partials(rt, h, self.w_gate, "side_gate")
+        g = rt.buffer("side_gated", (h.shape[0], self.dim), rt.dtype)
+        ops.gated_rows(z, S, batch.tokens, self.table, self.first, g)
+        stream.add_linear(g, self.w_proj)

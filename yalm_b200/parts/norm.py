@@ -30,15 +30,52 @@ class RMSNorm:
         if self.unit_offset:
             self.weight = self.weight + 1.0
 
+    def form(self):
+        """This norm as ``ops.norm_step`` takes it, for a block that norms a sublayer's output."""
+        return (ops.NORM_RMS, self.weight, None, 0.0, self.eps)
+
     def __call__(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
                  n_rows: Optional[int] = None, name: str = "normed") -> torch.Tensor:
         n = stream.x.shape[0] if rows is None else int(n_rows)
         out = self.rt.buffer(name, (n, self.size), self.rt.dtype)
+        if stream.due is not None:
+            return stream.read_norm(self.form(), out, rows=rows, n_rows=n_rows)
         ops.rmsnorm(stream.x, self.weight, out, self.eps, partials=stream.pending,
                     n_partials=stream.n_pending, rows=rows)
         if rows is None:
             stream.pending, stream.n_pending = None, 0     # folded into x by the kernel
         return out
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh:
+    """A norm that computes no mean and no variance: n(x) = tanh(alpha x) w + b, with a stored scalar
+    alpha and a weight and a bias per feature, all in 32 bits.  As a layer's input norm it is called
+    like the others; as the norm of a sublayer's output it hands its ``form`` to the stream."""
+
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.size = int(params["size"])
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def tensor_needs(self):
+        return {"weight": TensorNeed((self.size,), init="ones"), "bias": TensorNeed((self.size,), init="around_zero"),
+                "alpha": TensorNeed((), init="ones")}
+
+    def bind(self, tensors) -> None:
+        self.weight = self.rt.vector(tensors["weight"])
+        self.bias = self.rt.vector(tensors["bias"])
+        self.alpha = float(tensors["alpha"].to(torch.float32).reshape(-1)[0])
+
+    def form(self):
+        return (ops.NORM_TANH, self.weight, self.bias, self.alpha, 0.0)
+
+    def __call__(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
+                 n_rows: Optional[int] = None, name: str = "normed") -> torch.Tensor:
+        n = stream.x.shape[0] if rows is None else int(n_rows)
+        out = self.rt.buffer(name, (n, self.size), self.rt.dtype)
+        return stream.read_norm(self.form(), out, rows=rows, n_rows=n_rows)
 
 
 @register_norm("sum_rmsnorm")

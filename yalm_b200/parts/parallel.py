@@ -10,6 +10,10 @@ forms the residual sum.  The block must therefore be one that norms after the su
 params: ``hidden_size``, ``eps``, ``scale``, ``branches`` = [(name, PartSpec), ...]; a branch's
 tensors are the keys of its own part prefixed with "<name>.", and its norm weight is
 "<name>.out".  Cache needs of the branches are passed through under "<name>.<need name>".
+
+``branch_norm`` False: the branches are not normed; the result is sum_b scales[b] * branch_b
+(``scales``: one factor per branch, default ``scale`` for each), left on the stream for a block
+whose own norm takes the sum (``sum_rmsnorm``, or the output norm of a ``prepost_norm`` block).
 """
 from __future__ import annotations
 
@@ -40,7 +44,11 @@ class ParallelBranches:
         self.D = int(params["hidden_size"])
         self.eps = float(params["eps"])
         self.scale = float(params.get("scale", 1.0))
+        self.branch_norm = bool(params.get("branch_norm", True))
         self.names = [name for name, _ in params["branches"]]
+        self.scales = [float(v) for v in (params.get("scales") or [self.scale] * len(self.names))]
+        if len(self.scales) != len(self.names):
+            raise ValueError("parallel_branches: one scale per branch")
         if len(self.names) != 2 or len(set(self.names)) != 2:
             raise ValueError("parallel_branches takes two branches with different names")
         self.branches = {name: make_part(MIXERS, spec, rt) for name, spec in params["branches"]}
@@ -51,13 +59,14 @@ class ParallelBranches:
         for name, part in self.branches.items():
             for key, need in part.tensor_needs().items():
                 needs[f"{name}.{key}"] = need
-            needs[f"{name}.out"] = TensorNeed((self.D,), init="ones")
+            if self.branch_norm:
+                needs[f"{name}.out"] = TensorNeed((self.D,), init="ones")
         return needs
 
     def bind(self, tensors) -> None:
         for name, part in self.branches.items():
             part.bind({key: tensors[f"{name}.{key}"] for key in part.tensor_needs()})
-            self.out_norm[name] = self.rt.vector(tensors[f"{name}.out"])
+            self.out_norm[name] = self.rt.vector(tensors[f"{name}.out"]) if self.branch_norm else None
 
     def cache_need(self):
         needs = {}
@@ -88,7 +97,7 @@ class ParallelBranches:
 
     def forward(self, h, batch, stream, view, shared: bool = False):
         outs, later = [], []
-        for name in self.names:
+        for name, scale in zip(self.names, self.scales):
             part = self.branches[name]
             bs = _BranchStream(self.rt, name)
             w = part.forward(h, batch, bs, self._view_of(name, part, view), shared=shared)
@@ -96,7 +105,7 @@ class ParallelBranches:
                 later.append(w)
             if not bs.n:
                 raise RuntimeError(f"branch {name!r} left no output")
-            outs.append((bs.slices, bs.n, self.out_norm[name], self.scale))
+            outs.append((bs.slices, bs.n, self.out_norm[name], scale))
         stream.add_branches(outs, self.eps)
         if later:
             return lambda: [w() for w in later]

@@ -127,10 +127,15 @@ def yarn_frequencies(dims: int, base: float, scaling: Optional[dict]):
 class PartialRope:
     """Rotation of the first ``dims`` features of every head (the rest pass unchanged), in pairs
     (i, i + dims/2) (``layout`` "halves") or (2i, 2i + 1) ("neighbours"), by pos * f_i with
-    optional YaRN scaling; the angle is formed in 32 bits inside the kernel.  Its kernel also
+    optional YaRN scaling; the angle is formed in 32 bits inside the kernel.  ``scaling`` with
+    ``"kind": "llama3"`` (``factor``, ``low_freq_factor``, ``high_freq_factor``,
+    ``original_max_position_embeddings``) rescales the frequencies by wavelength bands instead, as the
+    ``rope`` encoding does.  Its kernel also
     norms q and k over their whole projections first when the mixer hands it the weights
-    (``norms``), and takes the values from the keys as projected when the product has no v
-    rows (``has_v`` False).  It has no per-step table: the mixer's products stay apart from it."""
+    (``norms``), takes the values from the keys as projected when the product has no v
+    rows (``has_v`` False), and with ``head_norm`` = (eps, size) divides every head of q and k by its
+    root mean square after the rotation.  It has no per-step table: the mixer's products stay apart
+    from it."""
 
     def __init__(self, params: dict, rt):
         self.rt = rt
@@ -141,16 +146,19 @@ class PartialRope:
             raise ValueError(f"rope_partial: layout {params.get('layout')!r} (halves or neighbours)")
         if self.dims % 2 or not 0 <= self.dims <= self.head_dim:
             raise ValueError(f"rope_partial: {self.dims} rotated features of a head of {self.head_dim}")
-        if self.dims:
-            freq, self.mult = yarn_frequencies(self.dims, float(params["base"]), params.get("scaling"))
+        scaling = params.get("scaling") or None
+        if self.dims and scaling and scaling.get("kind") == "llama3":
+            freq, self.mult = llama3_inv_freq(self.dims, float(params["base"]), scaling), 1.0
+        elif self.dims:
+            freq, self.mult = yarn_frequencies(self.dims, float(params["base"]), scaling)
         else:
             freq, self.mult = torch.zeros(1), 1.0
         self.freq = freq.to(rt.device)
 
     def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G, write_cache=True,
-                         norms=None, has_v=True, bias=None) -> None:
+                         norms=None, has_v=True, bias=None, head_norm=None) -> None:
         qn, kn, n_q, n_k, eps = norms if norms is not None else (None, None, 1, 1, 0.0)
         ops.qk_norm_rope_store(qkv, n_partials, qn, kn, n_q, n_k, eps, self.freq, self.dims,
                                self.neighbours, self.mult, batch, q_out, kv_step, view.k, view.v,
                                view.slot_pos, H, G, self.head_dim, has_v, view.capacity, write_cache,
-                               pages=view.pages, bias=bias)
+                               pages=view.pages, bias=bias, head_norm=head_norm)

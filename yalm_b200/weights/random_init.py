@@ -31,7 +31,8 @@ def random_tensors(needs: Dict[str, TensorNeed], seed: int, dtype: torch.dtype =
             if need.init == "identity":           # a square mixing matrix that starts as "every one keeps its own"
                 t = torch.eye(need.shape[-1], dtype=torch.float32, device=device).expand(need.shape).clone()
             else:
-                fill = {"ones": 1.0, "around_zero": 0.0, "fraction": 1.0 / max(1, need.shape[-1])}[need.init]
+                last = need.shape[-1] if len(need.shape) else 1
+                fill = {"ones": 1.0, "around_zero": 0.0, "fraction": 1.0 / max(1, last)}[need.init]
                 t = torch.full(need.shape, fill, dtype=torch.float32, device=device)
             if norm_jitter:
                 t += norm_jitter * torch.randn(need.shape, generator=gen, dtype=torch.float32,
