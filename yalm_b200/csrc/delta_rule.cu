@@ -6,15 +6,16 @@
 //  * delta_prep: q and k of every token and q/k head become unit vectors (x / sqrt(sum x^2 + 1e-6)),
 //    q times 1/sqrt(dk); beta = sigmoid(.); and the two low-rank projections' first halves go out in
 //    the storage type as the input of their second halves;
-//  * delta_decay: g = exp(-exp(A_h) softplus(z + dt)) per head and key channel, and the output gate
-//    sigmoid(.) per head and value channel;
+//  * delta_decay: the decay per head and key channel, kept as g - 1 = expm1(-exp(A_h) softplus(z + dt))
+//    (a decay close to 1 has few bits of its own left in g; S + (g - 1) S keeps them), and the output
+//    gate sigmoid(.) per head and value channel;
 //  * delta_scan: the recurrence.  As in the other scans of this library a block owns RC_COLS value
 //    columns of one (sequence, head) -- the columns of S are independent of one another --, a warp two
 //    of them and a lane RPT neighbouring rows; the step's tokens come through a three-stage cp.async
 //    ring.  Unlike a plain linear recurrence the write needs k.S first, so every token costs one
 //    all-reduce over the warp before its update; the outputs' sums are formed for 16 tokens at once.
 //
-// The activated row of a token, float32: [q: G dk | k: G dk | v: H dv | beta: H padded to 4 | g: H dk].
+// The activated row of a token, float32: [q: G dk | k: G dk | v: H dv | beta: H padded to 4 | g - 1: H dk].
 #include "api.h"
 #include "common.cuh"
 
@@ -70,7 +71,7 @@ __global__ void delta_decay_kernel(float* __restrict__ act, int row, int decay0,
   const int e_end = min(n_k + n_v, (int)(blockIdx.y + 1) * 1024);
   for (int e = blockIdx.y * 1024 + threadIdx.x; e < e_end; e += blockDim.x) {
     const float v = sum_slices(zr + e, n_partials, partial_stride);
-    if (e < n_k) act[(size_t)t * row + decay0 + e] = expf(-expf(a_log[e / dk]) * softplus_f(v + dt_bias[e]));
+    if (e < n_k) act[(size_t)t * row + decay0 + e] = expm1f(-expf(a_log[e / dk]) * softplus_f(v + dt_bias[e]));
     else gate[(size_t)t * n_v + (e - n_k)] = 1.0f / (1.0f + expf(-v));
   }
 }
@@ -101,7 +102,7 @@ delta_scan_kernel(const float* __restrict__ act, int row, const int* __restrict_
   const int slot = seq_slot[b];
   const int t0 = q_start[b], t1 = q_start[b + 1];
   const int hp = (H + 3) & ~3;
-  // rows beyond dk: q = k = 0 for ever (never copied over), so whatever their decay, their state stays zero
+  // rows beyond dk: q = k = 0 for ever (never copied over), so their state stays zero
   if (dk < DKP) {
     for (int i = threadIdx.x; i < DR_STAGES * DR_TOK * PER_TOK; i += blockDim.x) stage[i] = 0.f;
     __syncthreads();
@@ -176,7 +177,7 @@ delta_scan_kernel(const float* __restrict__ act, int row, const int* __restrict_
           const float gi = gg[r], ki = kk[r];
 #pragma unroll
           for (int c = 0; c < DR_CPW; ++c) {
-            S[r][c] *= gi;
+            S[r][c] = fmaf(gi, S[r][c], S[r][c]);
             kd[c] = fmaf(ki, S[r][c], kd[c]);
           }
         }

@@ -3,11 +3,13 @@
 //   a = exp(-c r softplus(lam)),   S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t,   out_t = S_t y_t
 // with y = gelu(Wy h + by) the block's other branch.  S is one 32-bit float per channel and sequence.
 // Two kernels, all arithmetic 32-bit:
-//  * rglru_gates: every token and channel in parallel: a, b = sqrt(1 - a^2) i u, and y;
+//  * rglru_gates: every token and channel in parallel: log a, b = sqrt(1 - a^2) i u, and y;
 //  * rglru_scan: the recurrence S_t = a_t S_(t-1) + b_t.  A block owns 32 channels of one sequence
 //    and cuts the step's tokens into RG_CHUNKS runs; each run is first composed into one (A, B) pair
 //    (S_out = A S_in + B), the runs' pairs are chained from the sequence's state, and a second pass
-//    over the run writes S_t y_t.  1 - a^2 is formed as -expm1(2 log a).
+//    over the run writes S_t y_t.  A decay close to 1 has few bits of its own left in a, and a state
+//    that lives for a thousand tokens collects that error: so a step is S + expm1(log a) S + b, a
+//    run's A is exp(sum of log a), and 1 - a^2 is -expm1(2 log a).
 #include "api.h"
 #include "common.cuh"
 
@@ -17,7 +19,7 @@ constexpr int RG_CHUNKS = 8;
 
 // grid (tokens, parts of the channels).  gates: float32 [blocks][tokens][2 bw] (the r logits of a
 // block's channels, then its i logits); yx: slices [.][tokens][yx_row] with the y logits at column 0;
-// coef [3][tokens][width] receives a, b, y.
+// coef [3][tokens][width] receives log a, b, y.
 __global__ void rglru_gates_kernel(const float* __restrict__ gates, const float* __restrict__ ra_bias,
                                    const float* __restrict__ ri_bias, const float* __restrict__ lam,
                                    const float* __restrict__ u, const float* __restrict__ yx, int n_partials,
@@ -34,12 +36,11 @@ __global__ void rglru_gates_kernel(const float* __restrict__ gates, const float*
   const float r = 1.0f / (1.0f + expf(-(g[0] + ba)));
   const float i = 1.0f / (1.0f + expf(-(g[bw] + bi)));
   const float log_a = -c_decay * r * sp;
-  const float a = expf(log_a);
   const float b = sqrtf(-expm1f(2.0f * log_a)) * i * u[(size_t)t * width + c];
   const float yv = sum_slices(yx + (size_t)t * yx_row + c, n_partials, partial_stride) + by;
   const float y = 0.5f * yv * (1.0f + tanhf(0.7978845608028654f * (yv + 0.044715f * yv * yv * yv)));
   const size_t plane = (size_t)n_tokens * width;
-  coef[(size_t)t * width + c] = a;
+  coef[(size_t)t * width + c] = log_a;
   coef[plane + (size_t)t * width + c] = b;
   coef[2 * plane + (size_t)t * width + c] = y;
 }
@@ -64,21 +65,21 @@ rglru_scan_kernel(const float* __restrict__ coef, const int* __restrict__ q_star
   const float* pa = coef + (size_t)t0 * width + c;
   const float* pb = pa + plane;
   const float* py = pb + plane;
-  float A = 1.f, B = 0.f;
+  float A = 0.f, B = 0.f;                              // A: the sum of log a
   if (live)
     for (int t = lo; t < hi; ++t) {
-      const float a = pa[(size_t)t * width];
-      A *= a;
-      B = fmaf(a, B, pb[(size_t)t * width]);
+      const float la = pa[(size_t)t * width];
+      A += la;
+      B = fmaf(expm1f(la), B, B) + pb[(size_t)t * width];
     }
-  sA[j][threadIdx.x] = A;
+  sA[j][threadIdx.x] = expm1f(A);
   sB[j][threadIdx.x] = B;
   __syncthreads();
   if (!live || lo >= hi) return;
   float S = state[(size_t)slot * width + c];
-  for (int jj = 0; jj < j; ++jj) S = fmaf(sA[jj][threadIdx.x], S, sB[jj][threadIdx.x]);
+  for (int jj = 0; jj < j; ++jj) S = fmaf(sA[jj][threadIdx.x], S, S) + sB[jj][threadIdx.x];
   for (int t = lo; t < hi; ++t) {
-    S = fmaf(pa[(size_t)t * width], S, pb[(size_t)t * width]);
+    S = fmaf(expm1f(pa[(size_t)t * width]), S, S) + pb[(size_t)t * width];
     out[(size_t)(t0 + t) * width + c] = from_float<T>(S * py[(size_t)t * width]);
   }
   if (hi == ql) state[(size_t)slot * width + c] = S;
