@@ -115,18 +115,26 @@ def delta_rule(q, k, v, beta, decay, S):
 
 
 def route(z, correction, groups: int, keep: int, top: int, scale: float):
-    """z [E] router logits of one token -> (chosen experts, their weights)."""
+    """z [E] router logits of one token -> (chosen experts, their weights, margin): the margin is the
+    smallest gap between something chosen and the best thing not chosen (groups, then experts); a
+    16-bit computation may rightly decide a call that close the other way."""
     s = torch.sigmoid(z)
     choice = s + correction
     E = z.numel()
     per = E // groups
     gs = choice.view(groups, per).topk(min(2, per), -1).values.sum(-1)
-    kept = gs.topk(keep).indices
+    order = gs.argsort(descending=True)
+    kept = order[:keep]
+    margin = float(gs[order[keep - 1]] - gs[order[keep]]) if keep < groups else float("inf")
     mask = torch.full((groups, per), float("-inf"), dtype=z.dtype)
     mask[kept] = 0.0
-    chosen = (choice + mask.view(-1)).topk(top).indices
+    cand = choice + mask.view(-1)
+    ranked = cand.argsort(descending=True)
+    chosen = ranked[:top]
+    if top < keep * per:
+        margin = min(margin, float(cand[ranked[top - 1]] - cand[ranked[top]]))
     w = s[chosen]
-    return chosen, w / (w.sum() + 1e-20) * scale
+    return chosen, w / (w.sum() + 1e-20) * scale, margin
 
 
 class PlainSamulorn:
@@ -144,6 +152,7 @@ class PlainSamulorn:
         else:
             self.runs = list(range(n))
         self.taps = None                                   # called as taps(run index, x [T, D]) after a layer run
+        self.margins: List[float] = []                     # of every routing decision made, in order
 
     def new_state(self) -> dict:
         return {"pos": 0, "runs": [dict() for _ in self.runs]}
@@ -226,8 +235,10 @@ class PlainSamulorn:
         z = h @ w[p + "router"].T
         out = torch.zeros_like(h)
         for t in range(h.shape[0]):
-            chosen, weights = route(z[t], w[p + "correction"], int(r["groups"]["count"]), int(r["groups"]["keep"]),
-                                    int(r["top"]), float(r["scale"]))
+            g = r.get("groups") or {"count": 1, "keep": 1}
+            chosen, weights, margin = route(z[t], w[p + "correction"], int(g["count"]), int(g["keep"]),
+                                            int(r["top"]), float(r.get("scale", 1.0)))
+            self.margins.append(margin)
             for e, wt in zip(chosen.tolist(), weights):
                 out[t] += wt * self._glu(f"{p}e{e}.", h[t:t + 1])[0]
         return out
