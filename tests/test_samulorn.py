@@ -35,7 +35,7 @@ def test_run_order_of_a_loop():
     order = lambda d: [e.layer for e in config_from_dict(d).to_spec().run_order]
     assert order(SAMU_A) == [0, 1, 2, 1, 2]
     assert order(SAMU_B) == [0, 1]
-    assert order(SAMU_C) == [0, 1, 0, 1, 0, 1]
+    assert order(SAMU_C) == [0, 1, 0, 1]
     d = copy.deepcopy(SAMU_A)
     d["loop"] = None
     assert order(d) == [0, 1, 2]
