@@ -435,7 +435,54 @@ NEKOTAR_SIZES = {
                       lat_vdim=128, kv_rank=192, att_heads=32, att_kv=8, att_dim=128, window=2048, keep=128,
                       ff=11008, pattern="wlaw", vocab=32000, mult=0.7),
 }
-DESIGNS = {"golulix": (DESIGN_SIZES, golulix_config, dense_twin),
+def samulorn_config(width, d_heads, d_kv, d_dim, d_vdim, rank, heads, kv_heads, head_dim, rot_dims, rec_width,
+                    rec_blocks, ff, experts, top, groups, keep, expert_ff, side_dim, pattern, vocab):
+    """A Samulorn configuration with layers of the sizes a served model has (random weights):
+    ``pattern`` is a string of "d" (a gated-delta-rule layer with a dense feed-forward) and "p"
+    (attention beside a recurrent unit, with routed experts of which a token uses as wide a
+    feed-forward as the dense one)."""
+    layers = []
+    for c in pattern:
+        if c == "d":
+            layers.append({"type": "channel_delta", "mlp": {"kind": "dense", "ff": ff},
+                           "mixer": {"heads": d_heads, "kv_heads": d_kv, "dim": d_dim, "vdim": d_vdim, "conv": 4,
+                                     "decay_rank": rank, "gate_rank": rank}})
+        else:
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": 4,
+                    "scale": float(head_dim) ** -0.5,
+                    "rot": {"base": 5e5, "dims": rot_dims,
+                            "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            layers.append({"type": "parallel",
+                           "mixer": {"left": left, "right": {"width": rec_width, "blocks": rec_blocks, "conv": 4},
+                                     "left_scale": 1.0, "right_scale": 1.0},
+                           "mlp": {"kind": "moe", "expert": {"ff": expert_ff},
+                                   "router": {"experts": experts, "top": top, "scale": 2.0,
+                                              "groups": {"count": groups, "keep": keep}}}})
+    return {"architecture": "Samulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(width) ** 0.5}, "token_side": {"dim": side_dim}, "layers": layers}
+
+
+def samulorn_twin(width, d_heads, d_kv, d_dim, d_vdim, rank, heads, kv_heads, head_dim, rot_dims, rec_width,
+                  rec_blocks, ff, experts, top, groups, keep, expert_ff, side_dim, pattern, vocab):
+    """The closest model the library had before: the Llama / Mistral decoder with the same width,
+    layers and feed-forward and the attention branch's heads, causal without a window."""
+    return {"architectures": ["LlamaForCausalLM"], "hidden_size": width, "intermediate_size": ff,
+            "num_hidden_layers": len(pattern), "num_attention_heads": heads, "num_key_value_heads": kv_heads,
+            "head_dim": head_dim, "vocab_size": vocab, "max_position_embeddings": 32768, "rms_norm_eps": 1e-6,
+            "rope_theta": 500000.0, "tie_word_embeddings": True, "hidden_act": "silu", "bos_token_id": 1,
+            "eos_token_id": 2}
+
+
+SAMULORN_SIZES = {
+    "w2048-dpdp": dict(width=2048, d_heads=16, d_kv=16, d_dim=128, d_vdim=128, rank=64, heads=16, kv_heads=4,
+                       head_dim=128, rot_dims=64, rec_width=2048, rec_blocks=16, ff=5632, experts=32, top=4,
+                       groups=4, keep=2, expert_ff=1408, side_dim=128, pattern="dpdp", vocab=32000),
+    "w4096-dpd": dict(width=4096, d_heads=32, d_kv=8, d_dim=128, d_vdim=128, rank=128, heads=32, kv_heads=8,
+                      head_dim=128, rot_dims=128, rec_width=4096, rec_blocks=16, ff=11008, experts=64, top=6,
+                      groups=8, keep=4, expert_ff=1792, side_dim=256, pattern="dpd", vocab=32000),
+}
+DESIGNS = {"samulorn": (SAMULORN_SIZES, samulorn_config, samulorn_twin),
+           "golulix": (DESIGN_SIZES, golulix_config, dense_twin),
            "rudazen": (RUDAZEN_SIZES, rudazen_config, rudazen_twin),
            "nekotar": (NEKOTAR_SIZES, nekotar_config, nekotar_twin)}
 
@@ -468,7 +515,10 @@ def compare_designs(args, pk):
                 t_flops = prefill_flops(lm, T) / (pk["bf16_tflops"] * 1e12)
                 # (a routed design reaches more experts with more tokens: one "sequence" per token
                 # counts that; any other design reads its weights once and one sequence's state)
-                t_bytes = lm.model.step_bytes([1] * T if args.design == "golulix" else [T]) / (pk["hbm_gbs"] * 1e9)
+                if args.design == "golulix":
+                    t_bytes = lm.model.step_bytes([1] * T) / (pk["hbm_gbs"] * 1e9)
+                else:
+                    t_bytes = lm.model.step_bytes([T], n_tokens=T) / (pk["hbm_gbs"] * 1e9)
                 r[f"prefill_{T}"] = {"tokens_s": p["value"], "ms": p["ms"], "flops_frac": p["frac"],
                                      "bound": "flops" if t_flops >= t_bytes else "hbm",
                                      "roofline_frac": max(t_flops, t_bytes) / (p["ms"] / 1e3)}
@@ -581,7 +631,7 @@ def main():
                          "beside the dense decoder at equal sizes (random weights, a few layers)")
     ap.add_argument("--design", default="golulix", choices=sorted(DESIGNS),
                     help="with --compare-designs: which design runs beside the dense decoder")
-    ap.add_argument("--design-size", default=None, choices=sorted(set(DESIGN_SIZES) | set(RUDAZEN_SIZES) | set(NEKOTAR_SIZES)),
+    ap.add_argument("--design-size", default=None, choices=sorted(set(DESIGN_SIZES) | set(RUDAZEN_SIZES) | set(NEKOTAR_SIZES) | set(SAMULORN_SIZES)),
                     help="with --compare-designs: one of the design's sizes instead of all")
     args = ap.parse_args()
 

@@ -113,10 +113,11 @@ class Model:
         return out
 
     # -- what a step costs (for roofline figures) ------------------------------
-    def step_bytes(self, contexts) -> int:
+    def step_bytes(self, contexts, n_tokens: Optional[int] = None) -> int:
         """Bytes a decode step of sequences with these context lengths has to read:
         every weight once (of the embedding table one row per sequence) and the cache
-        of the live sequences."""
+        of the live sequences.  ``n_tokens``: the step's tokens when they are more than one per
+        sequence (a prompt: parts that read some of their weights per token count by it)."""
         esz = torch.empty((), dtype=self.rt.dtype).element_size()
         needs = self.tensor_needs()                  # declared shapes: no device needed
         table_name = self.spec.embedding.tensors.get("weight")
@@ -132,7 +133,7 @@ class Model:
             for part, _ in self.layers[e.layer].parts():
                 f = getattr(part, "step_weight_bytes", None)
                 if f is not None:
-                    total += f(len(contexts), esz)
+                    total += f(len(contexts) if n_tokens is None else int(n_tokens), esz)
         for name, need in needs.items():
             if name in own:
                 continue
