@@ -70,7 +70,7 @@ __global__ void delta_decay_kernel(float* __restrict__ act, int row, int decay0,
   const float* zr = z + (size_t)t * (n_k + n_v);
   const int e_end = min(n_k + n_v, (int)(blockIdx.y + 1) * 1024);
   for (int e = blockIdx.y * 1024 + threadIdx.x; e < e_end; e += blockDim.x) {
-    const float v = sum_slices(zr + e, n_partials, partial_stride);
+    const float v = n_partials == 1 ? zr[e] : sum_slices(zr + e, n_partials, partial_stride);
     if (e < n_k) act[(size_t)t * row + decay0 + e] = expm1f(-expf(a_log[e / dk]) * softplus_f(v + dt_bias[e]));
     else gate[(size_t)t * n_v + (e - n_k)] = 1.0f / (1.0f + expf(-v));
   }
@@ -83,6 +83,25 @@ __device__ __forceinline__ void dr_cp_async(float* dst, const float* src) {
 __device__ __forceinline__ void dr_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void dr_cp_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// A lane's RPT neighbouring rows of a staged vector, as one 8- or 16-byte access per two or four rows:
+// single-float loads at a stride of RPT floats would meet RPT-fold bank conflicts.
+template <int RPT>
+__device__ __forceinline__ void lane_rows(const float* __restrict__ p, float* out) {
+  if constexpr (RPT % 4 == 0) {
+#pragma unroll
+    for (int r = 0; r < RPT; r += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(p + r);
+      out[r] = v.x; out[r + 1] = v.y; out[r + 2] = v.z; out[r + 3] = v.w;
+    }
+  } else if constexpr (RPT == 2) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    out[0] = v.x; out[1] = v.y;
+  } else {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) out[r] = p[r];
+  }
 }
 
 // VEC: floats per copy (4 when every run starts on a 16-byte boundary, else 1)
@@ -160,44 +179,52 @@ delta_scan_kernel(const float* __restrict__ act, int row, const int* __restrict_
     const int nt = min(DR_TOK, t1 - base);
     const float* sg = stage + (size_t)(g % DR_STAGES) * DR_TOK * PER_TOK;
     float o[DR_TOK][DR_CPW];
+    auto token = [&](int tt) {
+      const float* qq = sg + tt * PER_TOK + lane * RPT;
+      const float* kk = qq + DKP;
+      const float* gg = qq + 2 * DKP;
+      const float beta = sg[tt * PER_TOK + 3 * DKP + DR_COLS];
+      float vj[DR_CPW], kd[DR_CPW], kr[RPT], qr[RPT], gr[RPT];
+      lane_rows<RPT>(qq, qr);
+      lane_rows<RPT>(kk, kr);
+      lane_rows<RPT>(gg, gr);
 #pragma unroll
-    for (int tt = 0; tt < DR_TOK; ++tt) {
+      for (int c = 0; c < DR_CPW; ++c) { vj[c] = sg[tt * PER_TOK + 3 * DKP + w * DR_CPW + c]; kd[c] = 0.f; }
 #pragma unroll
-      for (int c = 0; c < DR_CPW; ++c) o[tt][c] = 0.f;
-      if (tt < nt) {
-        const float* qq = sg + tt * PER_TOK + lane * RPT;
-        const float* kk = qq + DKP;
-        const float* gg = qq + 2 * DKP;
-        const float beta = sg[tt * PER_TOK + 3 * DKP + DR_COLS];
-        float vj[DR_CPW], kd[DR_CPW];
+      for (int r = 0; r < RPT; ++r) {
+        const float gi = gr[r];
 #pragma unroll
-        for (int c = 0; c < DR_CPW; ++c) { vj[c] = sg[tt * PER_TOK + 3 * DKP + w * DR_CPW + c]; kd[c] = 0.f; }
-#pragma unroll
-        for (int r = 0; r < RPT; ++r) {
-          const float gi = gg[r], ki = kk[r];
-#pragma unroll
-          for (int c = 0; c < DR_CPW; ++c) {
-            S[r][c] = fmaf(gi, S[r][c], S[r][c]);
-            kd[c] = fmaf(ki, S[r][c], kd[c]);
-          }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-          for (int c = 0; c < DR_CPW; ++c) kd[c] += __shfl_xor_sync(0xffffffffu, kd[c], off);
-        float u[DR_CPW];
-#pragma unroll
-        for (int c = 0; c < DR_CPW; ++c) u[c] = beta * (vj[c] - kd[c]);
-#pragma unroll
-        for (int r = 0; r < RPT; ++r) {
-          const float ki = kk[r], qi = qq[r];
-#pragma unroll
-          for (int c = 0; c < DR_CPW; ++c) {
-            S[r][c] = fmaf(ki, u[c], S[r][c]);
-            o[tt][c] = fmaf(S[r][c], qi, o[tt][c]);
-          }
+        for (int c = 0; c < DR_CPW; ++c) {
+          S[r][c] = fmaf(gi, S[r][c], S[r][c]);
+          kd[c] = fmaf(kr[r], S[r][c], kd[c]);
         }
       }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int c = 0; c < DR_CPW; ++c) kd[c] += __shfl_xor_sync(0xffffffffu, kd[c], off);
+      float u[DR_CPW];
+#pragma unroll
+      for (int c = 0; c < DR_CPW; ++c) u[c] = beta * (vj[c] - kd[c]);
+#pragma unroll
+      for (int r = 0; r < RPT; ++r)
+#pragma unroll
+        for (int c = 0; c < DR_CPW; ++c) {
+          S[r][c] = fmaf(kr[r], u[c], S[r][c]);
+          o[tt][c] = fmaf(S[r][c], qr[r], o[tt][c]);
+        }
+    };
+#pragma unroll
+    for (int tt = 0; tt < DR_TOK; ++tt)
+#pragma unroll
+      for (int c = 0; c < DR_CPW; ++c) o[tt][c] = 0.f;
+    if (nt == DR_TOK) {                                // a full group: no test between the tokens, so that a
+#pragma unroll                                         // token's rows are loaded while the one before is reduced
+      for (int tt = 0; tt < DR_TOK; ++tt) token(tt);
+    } else {
+#pragma unroll
+      for (int tt = 0; tt < DR_TOK; ++tt)
+        if (tt < nt) token(tt);
     }
     // the 32 lanes' partial sums of the group's 32 outputs: in every round a lane hands half of its
     // values to its partner and adds the partner's other half to its own

@@ -5,7 +5,7 @@
 // Two kernels, all arithmetic 32-bit:
 //  * rglru_gates: every token and channel in parallel: log a, b = sqrt(1 - a^2) i u, and y;
 //  * rglru_scan: the recurrence S_t = a_t S_(t-1) + b_t.  A block owns 32 channels of one sequence
-//    and cuts the step's tokens into RG_CHUNKS runs; each run is first composed into one (A, B) pair
+//    and cuts the step's tokens into RG_CHUNKS = 32 runs; each run is first composed into one (A, B) pair
 //    (S_out = A S_in + B), the runs' pairs are chained from the sequence's state, and a second pass
 //    over the run writes S_t y_t.  A decay close to 1 has few bits of its own left in a, and a state
 //    that lives for a thousand tokens collects that error: so a step is S + expm1(log a) S + b, a
@@ -15,7 +15,7 @@
 
 namespace yalm {
 
-constexpr int RG_CHUNKS = 8;
+constexpr int RG_CHUNKS = 32;
 
 // grid (tokens, parts of the channels).  gates: float32 [blocks][tokens][2 bw] (the r logits of a
 // block's channels, then its i logits); yx: slices [.][tokens][yx_row] with the y logits at column 0;
@@ -37,7 +37,8 @@ __global__ void rglru_gates_kernel(const float* __restrict__ gates, const float*
   const float i = 1.0f / (1.0f + expf(-(g[bw] + bi)));
   const float log_a = -c_decay * r * sp;
   const float b = sqrtf(-expm1f(2.0f * log_a)) * i * u[(size_t)t * width + c];
-  const float yv = sum_slices(yx + (size_t)t * yx_row + c, n_partials, partial_stride) + by;
+  const float* yp = yx + (size_t)t * yx_row + c;
+  const float yv = (n_partials == 1 ? yp[0] : sum_slices(yp, n_partials, partial_stride)) + by;
   const float y = 0.5f * yv * (1.0f + tanhf(0.7978845608028654f * (yv + 0.044715f * yv * yv * yv)));
   const size_t plane = (size_t)n_tokens * width;
   coef[(size_t)t * width + c] = log_a;
@@ -66,19 +67,44 @@ rglru_scan_kernel(const float* __restrict__ coef, const int* __restrict__ q_star
   const float* pb = pa + plane;
   const float* py = pb + plane;
   float A = 0.f, B = 0.f;                              // A: the sum of log a
-  if (live)
-    for (int t = lo; t < hi; ++t) {
+  if (live) {
+    int t = lo;
+    for (; t + 4 <= hi; t += 4) {                       // four tokens' loads and expm1 ahead of the chain
+      float la[4], bb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { la[u] = pa[(size_t)(t + u) * width]; bb[u] = pb[(size_t)(t + u) * width]; }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        A += la[u];
+        B = fmaf(expm1f(la[u]), B, B) + bb[u];
+      }
+    }
+    for (; t < hi; ++t) {
       const float la = pa[(size_t)t * width];
       A += la;
       B = fmaf(expm1f(la), B, B) + pb[(size_t)t * width];
     }
+  }
   sA[j][threadIdx.x] = expm1f(A);
   sB[j][threadIdx.x] = B;
   __syncthreads();
   if (!live || lo >= hi) return;
   float S = state[(size_t)slot * width + c];
   for (int jj = 0; jj < j; ++jj) S = fmaf(sA[jj][threadIdx.x], S, S) + sB[jj][threadIdx.x];
-  for (int t = lo; t < hi; ++t) {
+  int t = lo;
+  for (; t + 4 <= hi; t += 4) {
+    float la[4], bb[4], yy[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      la[u] = pa[(size_t)(t + u) * width]; bb[u] = pb[(size_t)(t + u) * width]; yy[u] = py[(size_t)(t + u) * width];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      S = fmaf(expm1f(la[u]), S, S) + bb[u];
+      out[(size_t)(t0 + t + u) * width + c] = from_float<T>(S * yy[u]);
+    }
+  }
+  for (; t < hi; ++t) {
     S = fmaf(expm1f(pa[(size_t)t * width]), S, S) + pb[(size_t)t * width];
     out[(size_t)(t0 + t) * width + c] = from_float<T>(S * py[(size_t)t * width]);
   }
