@@ -118,7 +118,8 @@ def test_short_conv_ragged_steps_and_state(ops, taps, channels):
             at += ql
 
 
-@pytest.mark.parametrize("H, G, dk, dv", [(4, 2, 16, 24), (1, 1, 64, 48), (3, 1, 20, 10), (2, 2, 128, 64), (6, 3, 40, 130)])
+@pytest.mark.parametrize("H, G, dk, dv", [(4, 2, 16, 24), (1, 1, 64, 48), (3, 1, 20, 10), (2, 2, 128, 64), (6, 3, 40, 130),
+                                         (2, 1, 96, 32), (1, 1, 256, 72), (2, 2, 130, 20)])
 def test_delta_rule_kernels(ops, H, G, dk, dv):
     g = torch.Generator().manual_seed(H * 1000 + dk)
     q_lens, slots = [37, 1, 18], [2, 0, 3]
