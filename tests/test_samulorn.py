@@ -11,8 +11,8 @@ import torch.nn.functional as F
 
 from plain_samulorn import (PlainSamulorn, causal_attention, delta_rule, dyt, gelu_tanh, over_rms,
                             rotary_frequencies, rotate_neighbours, route, short_conv)
-from samulorn_helpers import (CONFIGS, RANKS, SAMU_A, SAMU_B, SAMU_C, make_weights, needle_model, needle_tokens,
-                              plain_logits, random_tokens, weights_of, NEEDLE, PROBE)
+from samulorn_helpers import (CONFIGS, SAMU_A, SAMU_B, SAMU_C, needle_model, needle_tokens, plain_logits,
+                              random_tokens, weights_of)
 from yalm_b200.config import ConfigError, config_from_dict
 from yalm_b200.engine.lm import tensor_needs_of
 

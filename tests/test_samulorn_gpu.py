@@ -21,7 +21,6 @@ from trace_tools import (Trace, add_batches, add_tail, add_whole, compare, force
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DTYPES = ["float32", "bfloat16", "float16"]
-TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
 
 
 @pytest.fixture(scope="module")
